@@ -4,7 +4,8 @@ from .registry import (Architecture, register_architecture, registered_architect
 from .qwen3 import Qwen3Config
 from .kefetar import KefetarConfig
 from .mukenex import MukenexConfig
+from .torinex import TorinexConfig
 
 __all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "Architecture",
            "register_architecture", "registered_architectures", "resolve_architecture",
-           "Qwen3Config", "KefetarConfig", "MukenexConfig"]
+           "Qwen3Config", "KefetarConfig", "MukenexConfig", "TorinexConfig"]

@@ -15,6 +15,10 @@
 //     [q_lat (c_dim) | rotated (r)], where q_lat[h] = W_uk[h]^T q_plain[h] was multiplied before
 //     (q_lat: [nh, tokens, c_dim]), since q_plain . (W_uk[h] c) = (W_uk[h]^T q_plain) . c.
 //
+// (3) joint_heads_prepare: as (1), but the RMS norm of q runs over ALL of the token's q columns at once (nh * d, before
+//     they are split into heads; weights of that size), and so does the norm of k (nkv * d).  One block a token.  A
+//     layer that reads another layer's keys and values has only the q columns (`has_kv` 0) and stores nothing.
+//
 // Rotation: the pair (u, v) of a token at position p becomes (u cos a - v sin a, v cos a + u sin a) with
 // a = p * inv_freq[i] in float; pairs are (2i, 2i + 1) (`interleaved`) or (i, i + rot_dims / 2).
 // A slot outside the pool sets an error bit and the store is skipped; slot 0 (padding rows) stores nothing.
@@ -158,6 +162,74 @@ latent_prepare_kernel(const T* __restrict__ x, int in_stride, const T* __restric
   }
 }
 
+template <typename T>
+__global__ void __launch_bounds__(256)
+joint_heads_prepare_kernel(const T* __restrict__ x, int in_stride, const float* __restrict__ bias,
+                           const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                           const float* __restrict__ inv_freq, int rot_dims, int interleaved,
+                           const int* __restrict__ positions, const int* __restrict__ slots, int nh, int nkv, int d,
+                           int dv, int has_kv, int page_size, long long cache_slots, T* __restrict__ q_out,
+                           T* __restrict__ k_cache, T* __restrict__ v_cache, int* err) {
+  __shared__ float scratch[33];
+  extern __shared__ float jrow[];                    // q (nh * d), then k (nkv * d), then v (nkv * dv)
+  const int t = blockIdx.x;
+  const int nq = nh * d, nk = has_kv ? nkv * d : 0, nv = has_kv ? nkv * dv : 0;
+  const T* src = x + static_cast<size_t>(t) * in_stride;
+  float ssq = 0.0f, ssk = 0.0f;
+  for (int i = threadIdx.x; i < nq + nk + nv; i += blockDim.x) {
+    float v = to_f32<T>(src[i]);
+    if (bias != nullptr) v += bias[i];
+    jrow[i] = v;
+    if (i < nq) ssq = fmaf(v, v, ssq);
+    else if (i < nq + nk) ssk = fmaf(v, v, ssk);
+  }
+  ssq = block_sum(ssq, scratch);
+  const float rq = q_w != nullptr ? 1.0f / sqrtf(ssq / static_cast<float>(nq) + eps) : 1.0f;
+  float rk = 1.0f;
+  if (has_kv && k_w != nullptr) {
+    ssk = block_sum(ssk, scratch);
+    rk = 1.0f / sqrtf(ssk / static_cast<float>(nk) + eps);
+  }
+  for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
+    if (i < nq) { if (q_w != nullptr) jrow[i] = jrow[i] * rq * q_w[i]; }
+    else if (k_w != nullptr) jrow[i] = jrow[i] * rk * k_w[i - nq];
+  }
+  __syncthreads();
+  if (inv_freq != nullptr && rot_dims > 0) {
+    const int half = rot_dims >> 1;
+    const float pos = static_cast<float>(positions[t]);
+    for (int i = threadIdx.x; i < (nh + (has_kv ? nkv : 0)) * half; i += blockDim.x) {
+      const int h = i / half, p = i - h * half;
+      float* row = jrow + h * d;                    // q heads, then k heads: all d wide and contiguous
+      const int a = interleaved ? 2 * p : p, b = interleaved ? 2 * p + 1 : p + half;
+      float sn, cs;
+      sincosf(pos * inv_freq[p], &sn, &cs);
+      const float u = row[a], v = row[b];
+      row[a] = u * cs - v * sn;
+      row[b] = v * cs + u * sn;
+    }
+    __syncthreads();
+  }
+  T* qd = q_out + static_cast<size_t>(t) * nq;
+  for (int i = threadIdx.x; i < nq; i += blockDim.x) qd[i] = from_f32<T>(jrow[i]);
+  if (!has_kv || slots == nullptr) return;
+  const int slot = slots[t];
+  if (slot == 0) return;
+  if (slot < 0 || slot >= cache_slots) {
+    if (threadIdx.x == 0) atomicOr(err, B200_ERR_SLOT_RANGE);
+    return;
+  }
+  const int page = slot / page_size, offset = slot - page * page_size;
+  for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+    const int kvh = i / d, c = i - kvh * d;
+    k_cache[((static_cast<size_t>(page) * nkv + kvh) * page_size + offset) * d + c] = from_f32<T>(jrow[nq + i]);
+  }
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    const int kvh = i / dv, c = i - kvh * dv;
+    v_cache[((static_cast<size_t>(page) * nkv + kvh) * page_size + offset) * dv + c] = from_f32<T>(jrow[nq + nk + i]);
+  }
+}
+
 B200_EXPORT int b200_heads_prepare(const void* x, int dtype, int in_stride, const float* bias, const float* q_w,
                                    const float* k_w, float eps, const float* inv_freq, int rot_dims, int interleaved,
                                    const int* positions, const int* slots, int tokens, int nh, int nkv, int d, int dv,
@@ -208,5 +280,35 @@ B200_EXPORT int b200_latent_prepare(const void* x, int dtype, int in_stride, con
         err);
   else
     return B200_BAD_DTYPE;
+  return b200_check_launch();
+}
+
+// (3): norms over the whole q and the whole k projection.  has_kv 0: x holds q columns only, nothing is stored.
+B200_EXPORT int b200_joint_heads_prepare(const void* x, int dtype, int in_stride, const float* bias, const float* q_w,
+                                         const float* k_w, float eps, const float* inv_freq, int rot_dims,
+                                         int interleaved, const int* positions, const int* slots, int tokens, int nh,
+                                         int nkv, int d, int dv, int has_kv, int page_size, long long cache_slots,
+                                         void* q_out, void* k_cache, void* v_cache, int* err, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (nh <= 0 || nkv <= 0 || d <= 0 || dv <= 0 || rot_dims < 0 || rot_dims > d || (rot_dims & 1) || page_size <= 0)
+    return B200_BAD_SIZE;
+  const size_t smem = (static_cast<size_t>(nh) * d + (has_kv ? static_cast<size_t>(nkv) * (d + dv) : 0)) * sizeof(float);
+  if (smem > 200 * 1024) return B200_BAD_SIZE;
+#define B200_JOINT(T)                                                                                               \
+  do {                                                                                                              \
+    if (smem > 48 * 1024) {                                                                                         \
+      cudaError_t e = cudaFuncSetAttribute(joint_heads_prepare_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                           static_cast<int>(smem));                                                 \
+      if (e != cudaSuccess) return static_cast<int>(e);                                                             \
+    }                                                                                                               \
+    joint_heads_prepare_kernel<T><<<tokens, 256, smem, stream>>>(                                                   \
+        static_cast<const T*>(x), in_stride, bias, q_w, k_w, eps, inv_freq, rot_dims, interleaved, positions, slots, \
+        nh, nkv, d, dv, has_kv, page_size, cache_slots, static_cast<T*>(q_out), static_cast<T*>(k_cache),           \
+        static_cast<T*>(v_cache), err);                                                                             \
+  } while (0)
+  if (dtype == B200_F32) B200_JOINT(float);
+  else if (dtype == B200_BF16) B200_JOINT(__nv_bfloat16);
+  else return B200_BAD_DTYPE;
+#undef B200_JOINT
   return b200_check_launch();
 }

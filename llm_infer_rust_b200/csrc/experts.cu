@@ -1,14 +1,17 @@
-// A mixture of small gated feed-forward experts whose choice is a table lookup: the row of a token's id in an
-// integer table [vocab, top] names its experts, each with weight 1 / top.
+// A mixture of small gated feed-forward experts.  A token's experts come from a table lookup (the row of its id in
+// an integer table [vocab, top], each expert with weight 1 / top) or from a router (expert_router_kernel: 32-bit
+// logits, softmax or sigmoid scores, the best groups of neighbouring experts, the top experts among them, each with
+// its score as weight).
 //
-//   expert e:  y = W_down[e] (silu(W_gate[e] x) * (W_up[e] x))          out[t] = (1 / top) sum_k y_(t, k)
+//   expert e:  y = W_down[e] glu(W_gate[e] x, W_up[e] x)          out[t] = sum_k weight_(t, k) y_(t, k) [+ add[t]]
+//   glu(g, u) = silu(g) u,  or  g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit)
 //
-// Four kernels, nothing goes through the host (a step can be captured in a graph):
+// Four kernels behind the choice, nothing goes through the host (a step can be captured in a graph):
 //   expert_route       (token, choice) pairs sorted by expert: sorted_token[pos], pos_of_pair[pair], the experts'
 //                      ranges and the list of row tiles (expert, first row) that the products walk
-//   expert_gate_up     H[pos] = silu(gate) * up for every sorted pair, rows of x gathered by token
+//   expert_gate_up     H[pos] = glu(gate, up) for every sorted pair, rows of x gathered by token
 //   expert_down        Y[pos] = W_down[e] H[pos], in float
-//   expert_combine     out[t] = (sum over k in order of Y[pos_of_pair[t * top + k]]) / top, in float
+//   expert_combine     out[t] = sum over k in order of weight(t, k) Y[pos_of_pair[t * top + k]] (+ add[t]), in float
 //
 // Weights: gate_up [experts, 2 * ff, width] (an expert's gate rows, then its up rows), down [experts, width, ff].
 // float32: FFMA, every output accumulated over k in order (a pair's result does not depend on its place in a tile,
@@ -21,10 +24,19 @@
 constexpr int TM = 64, TN = 64;      // rows (sorted pairs) and columns of a tile
 
 // ------------------------------------------------------------------ routing
+// The expert of pair i = token * top + k: the router's choice if there is one, else the table's entry for the token id
+// (-1 for an id outside the table).
+__device__ __forceinline__ int pair_expert(const int* __restrict__ token_ids, const int* __restrict__ table, int vocab,
+                                           int top, const int* __restrict__ choice, int i) {
+  if (choice != nullptr) return choice[i];
+  const int id = token_ids[i / top];
+  return (id >= 0 && id < vocab) ? table[static_cast<size_t>(id) * top + i % top] : -1;
+}
+
 // one block; shared memory: 2 * experts + 1 ints
 __global__ void __launch_bounds__(1024)
 expert_route_kernel(const int* __restrict__ token_ids, const int* __restrict__ table, int vocab, int top, int experts,
-                    int tokens, int* __restrict__ sorted_token, int* __restrict__ pos_of_pair,
+                    const int* __restrict__ choice, int tokens, int* __restrict__ sorted_token, int* __restrict__ pos_of_pair,
                     int* __restrict__ expert_start, int* __restrict__ tile_expert, int* __restrict__ tile_first,
                     int* __restrict__ num_tiles, int tile_rows, int* err) {
   extern __shared__ int sm[];
@@ -34,8 +46,7 @@ expert_route_kernel(const int* __restrict__ token_ids, const int* __restrict__ t
   for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
   __syncthreads();
   for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
-    const int id = token_ids[i / top];
-    int e = (id >= 0 && id < vocab) ? table[static_cast<size_t>(id) * top + i % top] : -1;
+    int e = pair_expert(token_ids, table, vocab, top, choice, i);
     if (e < 0 || e >= experts) { atomicOr(err, B200_ERR_TOKEN_RANGE); e = 0; }
     atomicAdd(&count[e], 1);
   }
@@ -56,8 +67,7 @@ expert_route_kernel(const int* __restrict__ token_ids, const int* __restrict__ t
   for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
   __syncthreads();
   for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
-    const int id = token_ids[i / top];
-    int e = (id >= 0 && id < vocab) ? table[static_cast<size_t>(id) * top + i % top] : 0;
+    int e = pair_expert(token_ids, table, vocab, top, choice, i);
     if (e < 0 || e >= experts) e = 0;
     const int pos = start[e] + atomicAdd(&count[e], 1);
     sorted_token[pos] = i / top;
@@ -66,6 +76,19 @@ expert_route_kernel(const int* __restrict__ token_ids, const int* __restrict__ t
 }
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+
+// What joins an expert's gate and up projections.  kind 0: silu(g) u.  kind 1: g' sigmoid(alpha g') (u' + 1) with
+// g' = min(g, limit), u' = clamp(u, -limit, limit).
+struct GluAct {
+  int kind;
+  float limit, alpha;
+};
+__device__ __forceinline__ float glu_f(float g, float u, const GluAct a) {
+  if (a.kind == 0) return silu_f(g) * u;
+  g = fminf(g, a.limit);
+  u = fminf(fmaxf(u, -a.limit), a.limit);
+  return g / (1.0f + expf(-a.alpha * g)) * (u + 1.0f);
+}
 
 // ------------------------------------------------------------------ float32 products
 // GATED: C[pos][n] = silu(A . Wg[n]) * (A . Wu[n]) with A rows gathered by sorted_token; else C[pos][n] = A[pos] . W[n].
@@ -76,7 +99,7 @@ expert_gemm_f32_kernel(const float* __restrict__ A, int lda, const int* __restri
                        const float* __restrict__ W, long long w_expert_stride, int up_row_offset,
                        float* __restrict__ C, int N, int K, const int* __restrict__ expert_start,
                        const int* __restrict__ tile_expert, const int* __restrict__ tile_first,
-                       const int* __restrict__ num_tiles) {
+                       const int* __restrict__ num_tiles, const GluAct act) {
   constexpr int BK = 16;
   if (static_cast<int>(blockIdx.y) >= *num_tiles) return;
   __shared__ float As[BK][TM + 4];
@@ -139,7 +162,7 @@ expert_gemm_f32_kernel(const float* __restrict__ A, int lda, const int* __restri
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx * 4 + j;
       if (n >= N) continue;
-      if constexpr (GATED) C[static_cast<size_t>(r) * N + n] = silu_f(acc[0][i][j]) * acc[1][i][j];
+      if constexpr (GATED) C[static_cast<size_t>(r) * N + n] = glu_f(acc[0][i][j], acc[1][i][j], act);
       else C[static_cast<size_t>(r) * N + n] = acc[0][i][j];
     }
   }
@@ -156,7 +179,7 @@ expert_gemm_bf16_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int*
                         const __nv_bfloat16* __restrict__ W, long long w_expert_stride, int up_row_offset,
                         TO* __restrict__ C, int N, int K, const int* __restrict__ expert_start,
                         const int* __restrict__ tile_expert, const int* __restrict__ tile_first,
-                        const int* __restrict__ num_tiles) {
+                        const int* __restrict__ num_tiles, const GluAct act) {
   using namespace nvcuda;
   constexpr int BK = 64, LD = BK + 8, G = GATED ? 2 : 1;
   if (static_cast<int>(blockIdx.y) >= *num_tiles) return;
@@ -238,7 +261,7 @@ expert_gemm_bf16_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int*
   for (int j = 0; j < 2; ++j) {
     if constexpr (GATED) {          // both accumulators have one layout: element i of one meets element i of the other
 #pragma unroll
-      for (int i = 0; i < acc[0][j].num_elements; ++i) acc[0][j].x[i] = silu_f(acc[0][j].x[i]) * acc[G - 1][j].x[i];
+      for (int i = 0; i < acc[0][j].num_elements; ++i) acc[0][j].x[i] = glu_f(acc[0][j].x[i], acc[G - 1][j].x[i], act);
     }
     wmma::store_matrix_sync(&Cs[warp][0][j * 16], acc[0][j], 32 + 4, wmma::mem_row_major);
   }
@@ -252,15 +275,130 @@ expert_gemm_bf16_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int*
 }
 
 // ------------------------------------------------------------------ the experts' outputs back to the tokens
+// weight: one per pair, or null for `uniform` each.  add [tokens, width] (TA; a shared expert's output) joins the sum.
+template <typename TA>
 __global__ void __launch_bounds__(256)
 expert_combine_kernel(float* __restrict__ out, const float* __restrict__ Y, const int* __restrict__ pos_of_pair,
-                      int top, int width, float inv_top) {
+                      int top, int width, float uniform, const float* __restrict__ weight,
+                      const TA* __restrict__ add) {
   const size_t t = blockIdx.x;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     float s = 0.0f;
-    for (int k = 0; k < top; ++k) s += Y[static_cast<size_t>(pos_of_pair[t * top + k]) * width + c];
-    out[t * width + c] = s * inv_top;
+    if (weight == nullptr) {
+      for (int k = 0; k < top; ++k) s += Y[static_cast<size_t>(pos_of_pair[t * top + k]) * width + c];
+      s *= uniform;
+    } else {
+      for (int k = 0; k < top; ++k)
+        s = fmaf(weight[t * top + k], Y[static_cast<size_t>(pos_of_pair[t * top + k]) * width + c], s);
+    }
+    if (add != nullptr) s += to_f32<TA>(add[t * width + c]);
+    out[t * width + c] = s;
   }
+}
+
+// ------------------------------------------------------------------ the router
+// z[t][e] = W[e] . x[t] in float (FFMA, whatever the dtype of x and W), scores = softmax over all experts (or a
+// sigmoid of each), experts in `groups` equal groups of neighbours, a group's score its largest score, only experts
+// of the `keep` best groups can be chosen, the `top` largest of them are, each weighted by its score (divided by
+// the chosen scores' sum if `renormalize`).  Ties go to the lower index.
+// A block takes ROUTER_TOKENS tokens: warp w multiplies experts w, w + 8, .. for all of them (a row of W is read
+// once a block; a logit's additions do not depend on which other tokens share the block), then warp t chooses for
+// token t.  Shared memory: ROUTER_TOKENS * experts floats (logits, then scores) and as many ints.
+constexpr int ROUTER_TOKENS = 8, ROUTER_WARPS = 8;
+
+template <typename TX, typename TW>
+__global__ void __launch_bounds__(ROUTER_WARPS * 32)
+expert_router_kernel(const TX* __restrict__ x, const TW* __restrict__ W, int tokens, int width, int experts,
+                     int groups, int keep, int top, int sigmoid_scores, int renormalize, int* __restrict__ choice,
+                     float* __restrict__ weight) {
+  extern __shared__ float rsm[];
+  float* z = rsm;                                                   // [ROUTER_TOKENS][experts]
+  int* open = reinterpret_cast<int*>(rsm + ROUTER_TOKENS * experts);   // [ROUTER_TOKENS][experts]: may still be chosen
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t0 = blockIdx.x * ROUTER_TOKENS;
+  const int nt = min(ROUTER_TOKENS, tokens - t0);
+  for (int e = warp; e < experts; e += ROUTER_WARPS) {
+    float acc[ROUTER_TOKENS];
+#pragma unroll
+    for (int i = 0; i < ROUTER_TOKENS; ++i) acc[i] = 0.0f;
+    const TW* w = W + static_cast<size_t>(e) * width;
+    for (int k = lane; k < width; k += 32) {
+      const float wk = to_f32<TW>(w[k]);
+#pragma unroll
+      for (int i = 0; i < ROUTER_TOKENS; ++i)
+        if (i < nt) acc[i] = fmaf(wk, to_f32<TX>(x[static_cast<size_t>(t0 + i) * width + k]), acc[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < ROUTER_TOKENS; ++i) {
+      const float v = warp_sum(acc[i]);
+      if (lane == 0) z[i * experts + e] = v;
+    }
+  }
+  __syncthreads();
+  if (warp >= nt) return;
+  float* s = z + warp * experts;
+  int* can = open + warp * experts;
+  const int t = t0 + warp;
+  if (sigmoid_scores) {
+    for (int e = lane; e < experts; e += 32) s[e] = 1.0f / (1.0f + expf(-s[e]));
+  } else {
+    float m = -INFINITY;
+    for (int e = lane; e < experts; e += 32) m = fmaxf(m, s[e]);
+    m = warp_max(m);
+    float sum = 0.0f;
+    for (int e = lane; e < experts; e += 32) { s[e] = expf(s[e] - m); sum += s[e]; }
+    sum = warp_sum(sum);
+    for (int e = lane; e < experts; e += 32) s[e] = s[e] / sum;
+  }
+  for (int e = lane; e < experts; e += 32) can[e] = groups <= 1 ? 1 : 0;
+  __syncwarp();
+  const int per = experts / max(groups, 1);
+  // argmax over lanes of (value, lower index first)
+  auto best_of = [&](float v, int i) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+      if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+    }
+    return i;
+  };
+  if (groups > 1) {
+    // the keep best groups, one at a time; `can` of a group's first expert doubles as "group taken"
+    for (int r = 0; r < keep; ++r) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32) {
+        if (can[g * per] != 0) continue;
+        float gm = -INFINITY;
+        for (int j = 0; j < per; ++j) gm = fmaxf(gm, s[g * per + j]);
+        if (gm > bv || (gm == bv && g < bi)) { bv = gm; bi = g; }
+      }
+      const int g = best_of(bv, bi);
+      __syncwarp();
+      if (g != 0x7fffffff)
+        for (int j = lane; j < per; j += 32) can[g * per + j] = 1;
+      __syncwarp();
+    }
+  }
+  float total = 0.0f;
+  for (int r = 0; r < top; ++r) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32)
+      if (can[e] == 1 && (s[e] > bv || (s[e] == bv && e < bi))) { bv = s[e]; bi = e; }
+    const int e = best_of(bv, bi);
+    __syncwarp();
+    if (lane == 0) {
+      choice[static_cast<size_t>(t) * top + r] = e == 0x7fffffff ? -1 : e;
+      weight[static_cast<size_t>(t) * top + r] = e == 0x7fffffff ? 0.0f : s[e];
+      if (e != 0x7fffffff) can[e] = 2;
+    }
+    if (e != 0x7fffffff) total += s[e];
+    __syncwarp();
+  }
+  if (renormalize && lane == 0 && total > 0.0f)
+    for (int r = 0; r < top; ++r) weight[static_cast<size_t>(t) * top + r] /= total;
 }
 
 // ------------------------------------------------------------------ C interface
@@ -288,13 +426,36 @@ static RouteLayout route_layout(int* route, int pairs, int experts) {
   return r;
 }
 
+// Who names a token's experts and how their outputs are summed: a table row by token id with equal weights, or a
+// router's choices [tokens, top] with a weight each; `add` [tokens, width] (dtype add_dtype) joins the sum.
+struct ExpertChoice {
+  const int *token_ids, *table;
+  int vocab;
+  const int* choice;
+  const float* weight;
+  const void* add;
+  int add_dtype;
+};
+
+static int launch_combine(float* out, const float* y, const int* pos_of_pair, int tokens, int top, int width,
+                          const ExpertChoice& c, cudaStream_t stream) {
+  const float uniform = 1.0f / static_cast<float>(top);
+  if (c.add != nullptr && c.add_dtype == B200_BF16)
+    expert_combine_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(out, y, pos_of_pair, top, width, uniform, c.weight,
+                                                                     static_cast<const __nv_bfloat16*>(c.add));
+  else
+    expert_combine_kernel<float><<<tokens, 256, 0, stream>>>(out, y, pos_of_pair, top, width, uniform, c.weight,
+                                                             static_cast<const float*>(c.add));
+  return b200_check_launch();
+}
+
 // x [tokens, width] -> out [tokens, width] float32.  `h` holds pairs * ff elements of x's dtype, `y` pairs * width
 // floats, `route` b200_expert_route_ints(...) ints.
-B200_EXPORT int b200_table_experts(const void* x, int dtype, const int* token_ids, const int* table, int vocab, int top,
-                                   int experts, const void* gate_up, const void* down, int tokens, int width, int ff,
-                                   void* h, float* y, int* route, float* out, int* err, cudaStream_t stream) {
+static int run_experts(const void* x, int dtype, const ExpertChoice& c, int top, int experts, const void* gate_up,
+                       const void* down, int tokens, int width, int ff, const GluAct act, void* h, float* y, int* route,
+                       float* out, int* err, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (top <= 0 || experts <= 0 || width <= 0 || ff <= 0 || vocab <= 0) return B200_BAD_SIZE;
+  if (top <= 0 || experts <= 0 || width <= 0 || ff <= 0 || (c.choice == nullptr && c.vocab <= 0)) return B200_BAD_SIZE;
   const long long pairs_ll = static_cast<long long>(tokens) * top;
   if (pairs_ll > (1ll << 30) || (2 * experts + 1) * sizeof(int) > 48 * 1024) return B200_BAD_SIZE;
   const int pairs = static_cast<int>(pairs_ll);
@@ -304,8 +465,8 @@ B200_EXPORT int b200_table_experts(const void* x, int dtype, const int* token_id
   int *sorted_token = rl.sorted_token, *pos_of_pair = rl.pos_of_pair, *expert_start = rl.expert_start;
   int *tile_expert = rl.tile_expert, *tile_first = rl.tile_first, *num_tiles = rl.num_tiles;
   expert_route_kernel<<<1, 1024, (2 * experts + 1) * sizeof(int), stream>>>(
-      token_ids, table, vocab, top, experts, tokens, sorted_token, pos_of_pair, expert_start, tile_expert, tile_first,
-      num_tiles, TM, err);
+      c.token_ids, c.table, c.vocab, top, experts, c.choice, tokens, sorted_token, pos_of_pair, expert_start,
+      tile_expert, tile_first, num_tiles, TM, err);
   int rc = b200_check_launch();
   if (rc != 0) return rc;
   const dim3 g1((ff + TN - 1) / TN, tiles), g2((width + TN - 1) / TN, tiles);
@@ -313,22 +474,66 @@ B200_EXPORT int b200_table_experts(const void* x, int dtype, const int* token_id
   if (dtype == B200_F32) {
     expert_gemm_f32_kernel<true><<<g1, 256, 0, stream>>>(
         static_cast<const float*>(x), width, sorted_token, static_cast<const float*>(gate_up), gu_stride, ff,
-        static_cast<float*>(h), ff, width, expert_start, tile_expert, tile_first, num_tiles);
+        static_cast<float*>(h), ff, width, expert_start, tile_expert, tile_first, num_tiles, act);
     expert_gemm_f32_kernel<false><<<g2, 256, 0, stream>>>(
         static_cast<const float*>(h), ff, nullptr, static_cast<const float*>(down), dn_stride, 0, y, width, ff,
-        expert_start, tile_expert, tile_first, num_tiles);
+        expert_start, tile_expert, tile_first, num_tiles, act);
   } else if (dtype == B200_BF16) {
     expert_gemm_bf16_kernel<true, __nv_bfloat16><<<g1, 256, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(x), width, sorted_token, static_cast<const __nv_bfloat16*>(gate_up),
-        gu_stride, ff, static_cast<__nv_bfloat16*>(h), ff, width, expert_start, tile_expert, tile_first, num_tiles);
+        gu_stride, ff, static_cast<__nv_bfloat16*>(h), ff, width, expert_start, tile_expert, tile_first, num_tiles, act);
     expert_gemm_bf16_kernel<false, float><<<g2, 256, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(h), ff, nullptr, static_cast<const __nv_bfloat16*>(down), dn_stride, 0, y,
-        width, ff, expert_start, tile_expert, tile_first, num_tiles);
+        width, ff, expert_start, tile_expert, tile_first, num_tiles, act);
   } else {
     return B200_BAD_DTYPE;
   }
   rc = b200_check_launch();
   if (rc != 0) return rc;
-  expert_combine_kernel<<<tokens, 256, 0, stream>>>(out, y, pos_of_pair, top, width, 1.0f / static_cast<float>(top));
+  return launch_combine(out, y, pos_of_pair, tokens, top, width, c, stream);
+}
+
+B200_EXPORT int b200_table_experts(const void* x, int dtype, const int* token_ids, const int* table, int vocab, int top,
+                                   int experts, const void* gate_up, const void* down, int tokens, int width, int ff,
+                                   void* h, float* y, int* route, float* out, int* err, cudaStream_t stream) {
+  const ExpertChoice c = {token_ids, table, vocab, nullptr, nullptr, nullptr, B200_F32};
+  return run_experts(x, dtype, c, top, experts, gate_up, down, tokens, width, ff, GluAct{0, 0.0f, 0.0f}, h, y, route,
+                     out, err, stream);
+}
+
+// The router alone: choice [tokens, top] ints and weight [tokens, top] floats.  x_dtype / w_dtype: B200_F32 or
+// B200_BF16 each; the products are FFMA either way.
+B200_EXPORT int b200_expert_router(const void* x, int x_dtype, const void* w, int w_dtype, int tokens, int width,
+                                   int experts, int groups, int keep, int top, int sigmoid_scores, int renormalize,
+                                   int* choice, float* weight, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (width <= 0 || experts <= 0 || groups <= 0 || experts % groups || keep <= 0 || keep > groups || top <= 0 ||
+      top > keep * (experts / groups))
+    return B200_BAD_SIZE;
+  const size_t smem = static_cast<size_t>(ROUTER_TOKENS) * experts * (sizeof(float) + sizeof(int));
+  if (smem > 48 * 1024) return B200_BAD_SIZE;
+  const unsigned blocks = (tokens + ROUTER_TOKENS - 1) / ROUTER_TOKENS;
+#define B200_ROUTER(TX, TW)                                                                                          \
+  expert_router_kernel<TX, TW><<<blocks, ROUTER_WARPS * 32, smem, stream>>>(                                         \
+      static_cast<const TX*>(x), static_cast<const TW*>(w), tokens, width, experts, groups, keep, top, sigmoid_scores, \
+      renormalize, choice, weight)
+  if (x_dtype == B200_F32 && w_dtype == B200_F32) B200_ROUTER(float, float);
+  else if (x_dtype == B200_BF16 && w_dtype == B200_BF16) B200_ROUTER(__nv_bfloat16, __nv_bfloat16);
+  else if (x_dtype == B200_BF16 && w_dtype == B200_F32) B200_ROUTER(__nv_bfloat16, float);
+  else if (x_dtype == B200_F32 && w_dtype == B200_BF16) B200_ROUTER(float, __nv_bfloat16);
+  else return B200_BAD_DTYPE;
+#undef B200_ROUTER
   return b200_check_launch();
+}
+
+// Experts chosen by a router: choice and weight [tokens, top] (b200_expert_router), glu kind `act_kind` with `limit`
+// and `alpha`, `add` (null, or [tokens, width] of add_dtype: what every token gets besides, e.g. a shared expert).
+B200_EXPORT int b200_routed_experts(const void* x, int dtype, const int* choice, const float* weight, int top,
+                                    int experts, const void* gate_up, const void* down, int tokens, int width, int ff,
+                                    int act_kind, float limit, float alpha, const void* add, int add_dtype, void* h,
+                                    float* y, int* route, float* out, int* err, cudaStream_t stream) {
+  if (choice == nullptr || weight == nullptr || act_kind < 0 || act_kind > 1) return B200_BAD_SIZE;
+  const ExpertChoice c = {nullptr, nullptr, 0, choice, weight, add, add_dtype};
+  return run_experts(x, dtype, c, top, experts, gate_up, down, tokens, width, ff, GluAct{act_kind, limit, alpha}, h, y,
+                     route, out, err, stream);
 }

@@ -8,7 +8,7 @@
 //   a tile is (row tile rt, column tile): rows tile_first[rt] .. of X' (or of H) for the A operand, and the rows of
 //   expert tile_expert[rt] in the experts' stacked weights ([experts * rows per expert, K] as one matrix) for B;
 //   rows of the tile that belong to the next expert (or lie beyond the last pair) are computed and not stored.
-//   GATED  H[pos] = silu(gate) * up: 128 gate columns and the same 128 up columns per tile, bfloat16 out
+//   GATED  H[pos] = glu(gate, up) (silu(gate) * up or the clamped form, see experts.cu): 128 gate columns and the same 128 up columns per tile, bfloat16 out
 //   else   Y[pos] = H[pos] . W_down[e]^T: 256 columns per tile, float out
 // Every wait is bounded by the clock, as in the kernel it is built from.
 #include "experts.cu"
@@ -29,7 +29,8 @@ __global__ void __launch_bounds__(THREADS, 1)
 expert_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap wmap,
                            TO* __restrict__ out, int cols, int K, int w_rows_per_expert,
                            const int* __restrict__ expert_start, const int* __restrict__ tile_expert,
-                           const int* __restrict__ tile_first, const int* __restrict__ num_row_tiles, int* err) {
+                           const int* __restrict__ tile_first, const int* __restrict__ num_row_tiles, int* err,
+                           const GluAct act) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(ring + STAGES * STAGE_BYTES);
@@ -144,7 +145,7 @@ expert_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __gri
             TO* dst = out + static_cast<size_t>(row) * cols + col0;
             __align__(16) bf16 r[32];
 #pragma unroll
-            for (int e = 0; e < 32; ++e) r[e] = __float2bfloat16_rn(g[e] / (1.0f + expf(-g[e])) * u[e]);
+            for (int e = 0; e < 32; ++e) r[e] = __float2bfloat16_rn(glu_f(g[e], u[e], act));
             if (col0 + 32 <= cols && (cols % 8) == 0) {
 #pragma unroll
               for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dst + q * 8) = *reinterpret_cast<const uint4*>(r + q * 8);
@@ -167,21 +168,21 @@ expert_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __gri
   }
 }
 
-// The same as b200_table_experts for bfloat16 with width and ff multiples of 8; `xs` holds pairs * width more
-// elements (the gathered rows).  gate_up [experts * 2 ff, width] and down [experts * width, ff] as stacked matrices.
-B200_EXPORT int b200_table_experts_tcgen05(const void* x, const int* token_ids, const int* table, int vocab, int top,
-                                           int experts, const void* gate_up, const void* down, int tokens, int width,
-                                           int ff, void* xs, void* h, float* y, int* route, float* out, int* err,
-                                           cudaStream_t stream) {
+// The same as run_experts for bfloat16 with width and ff multiples of 8; `xs` holds pairs * width more elements (the
+// gathered rows).  gate_up [experts * 2 ff, width] and down [experts * width, ff] as stacked matrices.
+static int run_experts_tcgen05(const void* x, const ExpertChoice& c, int top, int experts, const void* gate_up,
+                               const void* down, int tokens, int width, int ff, const GluAct act, void* xs, void* h,
+                               float* y, int* route, float* out, int* err, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (top <= 0 || experts <= 0 || width <= 0 || ff <= 0 || vocab <= 0 || width % 8 || ff % 8) return B200_BAD_SIZE;
+  if (top <= 0 || experts <= 0 || width <= 0 || ff <= 0 || (c.choice == nullptr && c.vocab <= 0) || width % 8 || ff % 8)
+    return B200_BAD_SIZE;
   const long long pairs_ll = static_cast<long long>(tokens) * top;
   if (pairs_ll > (1ll << 30) || (2 * experts + 1) * sizeof(int) > 48 * 1024) return B200_BAD_SIZE;
   const int pairs = static_cast<int>(pairs_ll);
   const RouteLayout rl = route_layout(route, pairs, experts);
   expert_route_kernel<<<1, 1024, (2 * experts + 1) * sizeof(int), stream>>>(
-      token_ids, table, vocab, top, experts, tokens, rl.sorted_token, rl.pos_of_pair, rl.expert_start, rl.tile_expert,
-      rl.tile_first, rl.num_tiles, TC_ROWS, err);
+      c.token_ids, c.table, c.vocab, top, experts, c.choice, tokens, rl.sorted_token, rl.pos_of_pair, rl.expert_start,
+      rl.tile_expert, rl.tile_first, rl.num_tiles, TC_ROWS, err);
   int rc = b200_check_launch();
   if (rc != 0) return rc;
   gather_rows_kernel<<<pairs, 256, 0, stream>>>(static_cast<bf16*>(xs), static_cast<const bf16*>(x), rl.sorted_token, width);
@@ -205,11 +206,32 @@ B200_EXPORT int b200_table_experts_tcgen05(const void* x, const int* token_ids, 
   const int most_row_tiles = (pairs + TC_ROWS - 1) / TC_ROWS + experts;    // the real count is known on the device only
   const int g1 = min(sms, most_row_tiles * ((ff + 127) / 128)), g2 = min(sms, most_row_tiles * ((width + BN - 1) / BN));
   rc = b200_launch(expert_gemm_tcgen05_kernel<true, bf16>, dim3(g1), dim3(THREADS), smem, stream, 0, xs_map, gu_map,
-                   static_cast<bf16*>(h), ff, width, 2 * ff, rl.expert_start, rl.tile_expert, rl.tile_first, rl.num_tiles, err);
+                   static_cast<bf16*>(h), ff, width, 2 * ff, rl.expert_start, rl.tile_expert, rl.tile_first, rl.num_tiles,
+                   err, act);
   if (rc != 0) return rc;
   rc = b200_launch(expert_gemm_tcgen05_kernel<false, float>, dim3(g2), dim3(THREADS), smem, stream, 0, h_map, dn_map, y,
-                   width, ff, width, rl.expert_start, rl.tile_expert, rl.tile_first, rl.num_tiles, err);
+                   width, ff, width, rl.expert_start, rl.tile_expert, rl.tile_first, rl.num_tiles, err, act);
   if (rc != 0) return rc;
-  expert_combine_kernel<<<tokens, 256, 0, stream>>>(out, y, rl.pos_of_pair, top, width, 1.0f / static_cast<float>(top));
-  return b200_check_launch();
+  return launch_combine(out, y, rl.pos_of_pair, tokens, top, width, c, stream);
+}
+
+B200_EXPORT int b200_table_experts_tcgen05(const void* x, const int* token_ids, const int* table, int vocab, int top,
+                                           int experts, const void* gate_up, const void* down, int tokens, int width,
+                                           int ff, void* xs, void* h, float* y, int* route, float* out, int* err,
+                                           cudaStream_t stream) {
+  const ExpertChoice c = {token_ids, table, vocab, nullptr, nullptr, nullptr, B200_F32};
+  return run_experts_tcgen05(x, c, top, experts, gate_up, down, tokens, width, ff, GluAct{0, 0.0f, 0.0f}, xs, h, y,
+                             route, out, err, stream);
+}
+
+// b200_routed_experts on the tcgen05 products (bfloat16, width and ff multiples of 8).
+B200_EXPORT int b200_routed_experts_tcgen05(const void* x, const int* choice, const float* weight, int top, int experts,
+                                            const void* gate_up, const void* down, int tokens, int width, int ff,
+                                            int act_kind, float limit, float alpha, const void* add, int add_dtype,
+                                            void* xs, void* h, float* y, int* route, float* out, int* err,
+                                            cudaStream_t stream) {
+  if (choice == nullptr || weight == nullptr || act_kind < 0 || act_kind > 1) return B200_BAD_SIZE;
+  const ExpertChoice c = {nullptr, nullptr, 0, choice, weight, add, add_dtype};
+  return run_experts_tcgen05(x, c, top, experts, gate_up, down, tokens, width, ff, GluAct{act_kind, limit, alpha}, xs,
+                             h, y, route, out, err, stream);
 }

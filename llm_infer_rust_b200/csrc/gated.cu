@@ -198,12 +198,13 @@ B200_EXPORT int b200_sigmoid_gate_mul(void* out, const void* a, const void* g, i
 }
 
 // ------------------------------------------------------------------ activations, a joint norm with a gate, a cap
-enum : int { ACT_SILU = 1, ACT_GELU_ERF = 2, ACT_GELU_TANH = 3 };
+enum : int { ACT_SILU = 1, ACT_GELU_ERF = 2, ACT_GELU_TANH = 3, ACT_RELU_SQUARED = 4 };
 
 __device__ __forceinline__ float activate(float z, int act) {
   if (act == ACT_SILU) return z / (1.0f + expf(-z));
   if (act == ACT_GELU_ERF) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
   if (act == ACT_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+  if (act == ACT_RELU_SQUARED) { const float r = fmaxf(z, 0.0f); return r * r; }
   return z;
 }
 
@@ -266,7 +267,7 @@ __global__ void __launch_bounds__(256) tanh_cap_kernel(float* z, long long n, fl
 B200_EXPORT int b200_activate_columns(void* out, int out_stride, const void* x, int stride, int tokens, int columns,
                                       int act, int dtype, cudaStream_t stream) {
   if (tokens <= 0 || columns <= 0) return 0;
-  if (act < ACT_SILU || act > ACT_GELU_TANH || stride < columns || out_stride < columns) return B200_BAD_SIZE;
+  if (act < ACT_SILU || act > ACT_RELU_SQUARED || stride < columns || out_stride < columns) return B200_BAD_SIZE;
   if (columns % 8 == 0 && stride % 8 == 0 && out_stride % 8 == 0 && (dtype == B200_F32 || dtype == B200_BF16) &&
       (reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(x)) % 32 == 0) {
     const dim3 vgrid(tokens, (columns / 8 + 255) / 256);
@@ -309,5 +310,95 @@ B200_EXPORT int b200_tanh_cap(float* z, long long n, float cap, cudaStream_t str
   if (n <= 0) return 0;
   if (!(cap > 0.0f)) return B200_BAD_SIZE;
   tanh_cap_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(z, n, cap);
+  return b200_check_launch();
+}
+
+// ------------------------------------------------------------------ gate and up joined; an activation times a table row
+// out[t][c] = glu(gate_up[t][c], gate_up[t][ff + c]).  kind 0: silu(g) u.  kind 1: g' sigmoid(alpha g') (u' + 1) with
+// g' = min(g, limit), u' = clamp(u, -limit, limit).  Computed in float, rounded once.
+template <typename T>
+__global__ void __launch_bounds__(256)
+glu_columns_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int ff, int kind, float limit, float alpha) {
+  const size_t t = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= ff) return;
+  float g = to_f32<T>(gate_up[t * 2 * ff + c]), u = to_f32<T>(gate_up[t * 2 * ff + ff + c]);
+  float r;
+  if (kind == 0) {
+    r = g / (1.0f + expf(-g)) * u;
+  } else {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    r = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+  }
+  out[t * ff + c] = from_f32<T>(r);
+}
+
+// out[t][c] = act(z[t][c]) * table[ids[t]][column + c]: a gate on a token's row of a second embedding table.
+// An id outside the table sets the error bit and reads row 0.
+template <typename T>
+__global__ void __launch_bounds__(128)
+act_table_mul_kernel(T* __restrict__ out, const T* __restrict__ z, const T* __restrict__ table, const int* __restrict__ ids,
+                     int vocab, int table_width, int column, int dim, int act, int* err) {
+  const size_t t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) atomicOr(err, B200_ERR_TOKEN_RANGE);
+    id = 0;
+  }
+  const T* row = table + static_cast<size_t>(id) * table_width + column;
+  for (int c = threadIdx.x; c < dim; c += blockDim.x)
+    out[t * dim + c] = from_f32<T>(activate(to_f32<T>(z[t * dim + c]), act) * to_f32<T>(row[c]));
+}
+
+B200_EXPORT int b200_glu_columns(void* out, const void* gate_up, int tokens, int ff, int kind, float limit, float alpha,
+                                 int dtype, cudaStream_t stream) {
+  if (tokens <= 0 || ff <= 0) return 0;
+  if (kind < 0 || kind > 1) return B200_BAD_SIZE;
+  const dim3 grid(tokens, (ff + 255) / 256);
+  if (dtype == B200_F32)
+    glu_columns_kernel<float><<<grid, 256, 0, stream>>>(static_cast<float*>(out), static_cast<const float*>(gate_up), ff,
+                                                        kind, limit, alpha);
+  else if (dtype == B200_BF16)
+    glu_columns_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+        static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(gate_up), ff, kind, limit, alpha);
+  else
+    return B200_BAD_DTYPE;
+  return b200_check_launch();
+}
+
+B200_EXPORT int b200_act_table_mul(void* out, const void* z, const void* table, const int* ids, int tokens, int vocab,
+                                   int table_width, int column, int dim, int act, int dtype, int* err,
+                                   cudaStream_t stream) {
+  if (tokens <= 0 || dim <= 0) return 0;
+  if (act < ACT_SILU || act > ACT_RELU_SQUARED || vocab <= 0 || column < 0 || column + dim > table_width)
+    return B200_BAD_SIZE;
+  if (dtype == B200_F32)
+    act_table_mul_kernel<float><<<tokens, 128, 0, stream>>>(static_cast<float*>(out), static_cast<const float*>(z),
+                                                            static_cast<const float*>(table), ids, vocab, table_width,
+                                                            column, dim, act, err);
+  else if (dtype == B200_BF16)
+    act_table_mul_kernel<__nv_bfloat16><<<tokens, 128, 0, stream>>>(
+        static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(z), static_cast<const __nv_bfloat16*>(table),
+        ids, vocab, table_width, column, dim, act, err);
+  else
+    return B200_BAD_DTYPE;
+  return b200_check_launch();
+}
+
+// y[t][c] += bias[c], the sum taken in float and rounded once (a projection's bias where nothing else can take it).
+template <typename T>
+__global__ void __launch_bounds__(256) add_row_bias_kernel(T* __restrict__ y, const float* __restrict__ bias, int width) {
+  const size_t t = blockIdx.x;
+  for (int c = threadIdx.x; c < width; c += blockDim.x)
+    y[t * width + c] = from_f32<T>(to_f32<T>(y[t * width + c]) + bias[c]);
+}
+
+B200_EXPORT int b200_add_row_bias(void* y, const float* bias, int tokens, int width, int dtype, cudaStream_t stream) {
+  if (tokens <= 0 || width <= 0) return 0;
+  if (dtype == B200_F32) add_row_bias_kernel<float><<<tokens, 256, 0, stream>>>(static_cast<float*>(y), bias, width);
+  else if (dtype == B200_BF16)
+    add_row_bias_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(y), bias, width);
+  else return B200_BAD_DTYPE;
   return b200_check_launch();
 }

@@ -1582,12 +1582,12 @@ def sigmoid_gate_mul(a: torch.Tensor, packed: torch.Tensor, gate_column: int) ->
 
 
 # --------------------------------------------------------------------------- activations, joint norm with a gate, caps
-ACTIVATIONS = {"silu": 1, "gelu_erf": 2, "gelu_tanh": 3}
+ACTIVATIONS = {"silu": 1, "gelu_erf": 2, "gelu_tanh": 3, "relu_squared": 4}
 
 
 def activate(x: torch.Tensor, act: str, columns: Optional[int] = None, in_place: bool = False) -> torch.Tensor:
     """act(x) element by element on the first ``columns`` columns of x [tokens, width] (all by default): silu,
-    gelu_erf (the exact one) or gelu_tanh; computed in float, rounded once.  ``in_place``: x itself is changed."""
+    gelu_erf (the exact one), gelu_tanh or relu_squared (max(x, 0)^2); computed in float, rounded once.  ``in_place``: x itself is changed."""
     _cuda(x)
     _contig(x)
     if act not in ACTIVATIONS or x.dim() != 2:
@@ -1696,6 +1696,44 @@ def heads_prepare(x: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor, v
     _ok(rc, "heads_prepare")
 
 
+def joint_heads_prepare(x: torch.Tensor, q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
+                        v_cache: Optional[torch.Tensor], positions: torch.Tensor, slots: Optional[torch.Tensor],
+                        num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int, has_kv: bool = True,
+                        bias: Optional[torch.Tensor] = None, q_weight: Optional[torch.Tensor] = None,
+                        k_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
+                        inv_freq: Optional[torch.Tensor] = None, rot_dims: int = 0, interleaved: bool = True) -> None:
+    """As ``heads_prepare``, but the RMS norm of q runs over all of a token's q columns at once (before they are split
+    into heads; ``q_weight`` has num_heads * head_dim entries) and the norm of k over all of its k columns.
+    ``has_kv`` False: ``x`` holds the q columns only (a layer that reads another layer's keys and values); nothing is
+    stored and the caches may be None."""
+    _cuda(x, q_out, k_cache, v_cache, positions, slots, bias, q_weight, k_weight, inv_freq)
+    _contig(x, q_out, k_cache, v_cache, positions, slots, bias, q_weight, k_weight, inv_freq)
+    _f32(bias, q_weight, k_weight, inv_freq)
+    nq, nk, nv = num_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * v_head_dim
+    c = nq + (nk + nv if has_kv else 0)
+    if x.shape[1] < c or q_out.dtype != x.dtype or tuple(q_out.shape) != (x.shape[0], nq):
+        raise KernelError("joint_heads_prepare: the projection is too narrow, or q and projection differ")
+    page_size, cache_slots = 1, 0
+    if has_kv:
+        if k_cache is None or v_cache is None or k_cache.dtype != x.dtype or v_cache.dtype != x.dtype or \
+                tuple(k_cache.shape[1:]) != (num_kv_heads, k_cache.shape[2], head_dim) or \
+                tuple(v_cache.shape[1:]) != (num_kv_heads, k_cache.shape[2], v_head_dim):
+            raise KernelError("the cache must be [pages + 1, kv_heads, page_size, width] in the projection's dtype")
+        page_size, cache_slots = k_cache.shape[2], k_cache.shape[0] * k_cache.shape[2]
+    if (bias is not None and bias.numel() != c) or (q_weight is not None and q_weight.numel() != nq) or \
+            (has_kv and k_weight is not None and k_weight.numel() != nk):
+        raise KernelError("joint_heads_prepare: bias or norm weights of the wrong size")
+    if inv_freq is not None and inv_freq.numel() * 2 != rot_dims:
+        raise KernelError("one frequency for every rotated pair is needed")
+    rc = load_cuda_library("attention_prepare.cu").b200_joint_heads_prepare(
+        _p(x), _code(x), x.shape[1], _p(bias), _p(q_weight), _p(k_weight if has_kv else None), ctypes.c_float(eps),
+        _p(inv_freq), int(rot_dims if inv_freq is not None else 0), int(bool(interleaved)), _p(positions),
+        _p(slots if has_kv else None), x.shape[0], num_heads, num_kv_heads, head_dim, v_head_dim, int(bool(has_kv)),
+        page_size, ctypes.c_longlong(cache_slots), _p(q_out), _p(k_cache if has_kv else None),
+        _p(v_cache if has_kv else None), _p(error_word(x.device)), _stream())
+    _ok(rc, "joint_heads_prepare")
+
+
 def latent_prepare(x: torch.Tensor, q_lat: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor,
                    v_cache: Optional[torch.Tensor], latent_weight: torch.Tensor, eps: float, positions: torch.Tensor,
                    slots: Optional[torch.Tensor], num_heads: int, head_dim: int, rot_dim: int, latent_dim: int,
@@ -1727,8 +1765,33 @@ def latent_prepare(x: torch.Tensor, q_lat: torch.Tensor, q_out: torch.Tensor, k_
     _ok(rc, "latent_prepare")
 
 
-# --------------------------------------------------------------------------- experts chosen by a table
+# --------------------------------------------------------------------------- experts chosen by a table or a router
 EXPERTS_TCGEN05_FROM_PAIRS = 512      # steps with this many (token, expert) pairs take the tcgen05 products
+GLU_KINDS = {"silu": 0, "clamped_swish": 1}
+
+
+def _experts_buffers(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, top: int, what: str):
+    tokens, width = x.shape
+    experts, ff2, _ = gate_up.shape
+    ff = ff2 // 2
+    if gate_up.dtype != x.dtype or down.dtype != x.dtype or tuple(down.shape) != (experts, width, ff) \
+            or gate_up.shape[2] != width:
+        raise KernelError(f"{what}: sizes or dtypes do not fit")
+    lib = load_cuda_library("experts.cu")
+    lib.b200_expert_route_ints.restype = ctypes.c_longlong
+    pairs = tokens * top
+    route = torch.empty(int(lib.b200_expert_route_ints(tokens, top, experts)), dtype=torch.int32, device=x.device)
+    h = torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
+    y = torch.empty((pairs, width), dtype=torch.float32, device=x.device)
+    out = torch.empty((tokens, width), dtype=torch.float32, device=x.device)
+    return lib, experts, ff, pairs, route, h, y, out
+
+
+def _experts_on_tcgen05(x: torch.Tensor, ff: int, pairs: int, tensor_memory: Optional[bool]) -> bool:
+    fits = x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and ff % 8 == 0 and pairs >= 128
+    if tensor_memory and not fits:
+        raise KernelError("the tcgen05 experts take bfloat16 with width and ff multiples of 8")
+    return fits and (tensor_memory if tensor_memory is not None else pairs >= EXPERTS_TCGEN05_FROM_PAIRS)
 
 
 def table_experts(x: torch.Tensor, token_ids: torch.Tensor, table: torch.Tensor, gate_up: torch.Tensor,
@@ -1741,23 +1804,11 @@ def table_experts(x: torch.Tensor, token_ids: torch.Tensor, table: torch.Tensor,
     _contig(x, token_ids, table, gate_up, down)
     _i32(token_ids, table)
     tokens, width = x.shape
-    experts, ff2, _ = gate_up.shape
-    ff = ff2 // 2
     vocab, top = table.shape
-    if gate_up.dtype != x.dtype or down.dtype != x.dtype or tuple(down.shape) != (experts, width, ff) \
-            or gate_up.shape[2] != width or token_ids.numel() != tokens:
+    if token_ids.numel() != tokens:
         raise KernelError("table_experts: sizes or dtypes do not fit")
-    lib = load_cuda_library("experts.cu")
-    lib.b200_expert_route_ints.restype = ctypes.c_longlong
-    pairs = tokens * top
-    route = torch.empty(int(lib.b200_expert_route_ints(tokens, top, experts)), dtype=torch.int32, device=x.device)
-    h = torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
-    y = torch.empty((pairs, width), dtype=torch.float32, device=x.device)
-    out = torch.empty((tokens, width), dtype=torch.float32, device=x.device)
-    fits = x.dtype == torch.bfloat16 and width % 8 == 0 and ff % 8 == 0 and pairs >= 128
-    if tensor_memory and not fits:
-        raise KernelError("the tcgen05 experts take bfloat16 with width and ff multiples of 8")
-    if fits and (tensor_memory if tensor_memory is not None else pairs >= EXPERTS_TCGEN05_FROM_PAIRS):
+    lib, experts, ff, pairs, route, h, y, out = _experts_buffers(x, gate_up, down, top, "table_experts")
+    if _experts_on_tcgen05(x, ff, pairs, tensor_memory):
         xs = torch.empty((pairs, width), dtype=x.dtype, device=x.device)
         rc = load_cuda_library("experts_tcgen05.cu").b200_table_experts_tcgen05(
             _p(x), _p(token_ids), _p(table), vocab, top, experts, _p(gate_up), _p(down), tokens, width, ff, _p(xs),
@@ -1767,4 +1818,143 @@ def table_experts(x: torch.Tensor, token_ids: torch.Tensor, table: torch.Tensor,
     rc = lib.b200_table_experts(_p(x), _code(x), _p(token_ids), _p(table), vocab, top, experts, _p(gate_up), _p(down),
                                 tokens, width, ff, _p(h), _p(y), _p(route), _p(out), _p(error_word(x.device)), _stream())
     _ok(rc, "table_experts", 4)
+    return out
+
+
+def expert_router(x: torch.Tensor, weight: torch.Tensor, top: int, groups: int = 1, keep: int = 1,
+                  scores: str = "softmax", renormalize: bool = False):
+    """A router's choice for every token: logits = weight x in float (FFMA, whatever the dtypes), scores = softmax over
+    all experts (or ``sigmoid`` of each); the experts form ``groups`` equal groups of neighbours, a group's score is its
+    largest score, and only experts of the ``keep`` best groups can be chosen; the ``top`` largest of those are.
+    Returns (choice int32 [tokens, top], weights float32 [tokens, top]): the chosen experts' scores, divided by their
+    sum if ``renormalize``.  Ties go to the lower index."""
+    _cuda(x, weight)
+    _contig(x, weight)
+    tokens, width = x.shape
+    experts = weight.shape[0]
+    if weight.shape[1] != width or scores not in ("softmax", "sigmoid"):
+        raise KernelError("expert_router: the router's matrix does not fit, or unknown scores")
+    choice = torch.empty((tokens, top), dtype=torch.int32, device=x.device)
+    gains = torch.empty((tokens, top), dtype=torch.float32, device=x.device)
+    rc = load_cuda_library("experts.cu").b200_expert_router(
+        _p(x), _code(x), _p(weight), _code(weight), tokens, width, experts, int(groups), int(keep), int(top),
+        int(scores == "sigmoid"), int(bool(renormalize)), _p(choice), _p(gains), _stream())
+    _ok(rc, "expert_router")
+    return choice, gains
+
+
+def routed_experts(x: torch.Tensor, choice: torch.Tensor, gains: torch.Tensor, gate_up: torch.Tensor,
+                   down: torch.Tensor, glu: str = "silu", limit: float = 0.0, alpha: float = 1.0,
+                   add: Optional[torch.Tensor] = None, tensor_memory: Optional[bool] = None) -> torch.Tensor:
+    """out[t] = sum_k gains[t, k] down[e] glu(gate[e] x_t, up[e] x_t) (+ add[t]), e = choice[t, k]; float32
+    [tokens, width].  ``glu``: "silu" (silu(g) u) or "clamped_swish" (g' sigmoid(alpha g') (u' + 1), g' = min(g, limit),
+    u' = clamp(u, -limit, limit)).  ``add`` [tokens, width] (float32 or x's dtype) joins the sum in float: what every
+    token gets besides its experts.  Weights and the choice of product kernels as in ``table_experts``."""
+    _cuda(x, choice, gains, gate_up, down, add)
+    _contig(x, choice, gains, gate_up, down, add)
+    _i32(choice)
+    _f32(gains)
+    tokens, width = x.shape
+    top = choice.shape[1]
+    if glu not in GLU_KINDS or tuple(choice.shape) != (tokens, top) or tuple(gains.shape) != (tokens, top) or \
+            (add is not None and (tuple(add.shape) != (tokens, width) or add.dtype not in (torch.float32, x.dtype))):
+        raise KernelError("routed_experts: sizes or dtypes do not fit")
+    lib, experts, ff, pairs, route, h, y, out = _experts_buffers(x, gate_up, down, top, "routed_experts")
+    add_code = _code(add) if add is not None else F32
+    if _experts_on_tcgen05(x, ff, pairs, tensor_memory):
+        xs = torch.empty((pairs, width), dtype=x.dtype, device=x.device)
+        rc = load_cuda_library("experts_tcgen05.cu").b200_routed_experts_tcgen05(
+            _p(x), _p(choice), _p(gains), top, experts, _p(gate_up), _p(down), tokens, width, ff, GLU_KINDS[glu],
+            ctypes.c_float(limit), ctypes.c_float(alpha), _p(add), add_code, _p(xs), _p(h), _p(y), _p(route), _p(out),
+            _p(error_word(x.device)), _stream())
+        _ok(rc, "routed_experts_tcgen05", 5)
+        return out
+    rc = lib.b200_routed_experts(_p(x), _code(x), _p(choice), _p(gains), top, experts, _p(gate_up), _p(down), tokens,
+                                 width, ff, GLU_KINDS[glu], ctypes.c_float(limit), ctypes.c_float(alpha), _p(add),
+                                 add_code, _p(h), _p(y), _p(route), _p(out), _p(error_word(x.device)), _stream())
+    _ok(rc, "routed_experts", 4)
+    return out
+
+
+def glu_columns(gate_up: torch.Tensor, glu: str = "silu", limit: float = 0.0, alpha: float = 1.0) -> torch.Tensor:
+    """out = glu(gate_up[:, :F], gate_up[:, F:]) with the forms of ``routed_experts``; computed in float, rounded once."""
+    _cuda(gate_up)
+    _contig(gate_up)
+    tokens, width2 = gate_up.shape
+    if width2 % 2 or glu not in GLU_KINDS:
+        raise KernelError("glu_columns needs an even width and a known form")
+    out = torch.empty((tokens, width2 // 2), dtype=gate_up.dtype, device=gate_up.device)
+    rc = _gated().b200_glu_columns(_p(out), _p(gate_up), tokens, width2 // 2, GLU_KINDS[glu], ctypes.c_float(limit),
+                                   ctypes.c_float(alpha), _code(gate_up), _stream())
+    _ok(rc, "glu_columns")
+    return out
+
+
+def add_row_bias(y: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """y[t] += bias (float32, one per column), in place; the sum is taken in float and rounded once."""
+    _cuda(y, bias)
+    _contig(y, bias)
+    _f32(bias)
+    if y.dim() != 2 or bias.numel() != y.shape[1]:
+        raise KernelError("add_row_bias: one bias per column of y [tokens, width]")
+    rc = _gated().b200_add_row_bias(_p(y), _p(bias), y.shape[0], y.shape[1], _code(y), _stream())
+    _ok(rc, "add_row_bias")
+    return y
+
+
+def act_table_mul(z: torch.Tensor, act: str, table: torch.Tensor, ids: torch.Tensor, column: int) -> torch.Tensor:
+    """out[t, c] = act(z[t, c]) * table[ids[t], column + c]: a gate on a token's row of a second embedding table."""
+    _cuda(z, table, ids)
+    _contig(z, table, ids)
+    _i32(ids)
+    tokens, dim = z.shape
+    if act not in ACTIVATIONS or table.dtype != z.dtype or ids.numel() != tokens or column + dim > table.shape[1]:
+        raise KernelError("act_table_mul: sizes or dtypes do not fit")
+    out = torch.empty_like(z)
+    rc = _gated().b200_act_table_mul(_p(out), _p(z), _p(table), _p(ids), tokens, table.shape[0], table.shape[1],
+                                     int(column), dim, ACTIVATIONS[act], _code(z), _p(error_word(z.device)), _stream())
+    _ok(rc, "act_table_mul")
+    return out
+
+
+# --------------------------------------------------------------------------- a float stream with norms on the outputs
+def norm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, bias: Optional[torch.Tensor] = None,
+             cast_to: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """x <- x + (y + bias) / sqrt(mean((y + bias)^2) + eps) * weight, in place on the float32 stream x [tokens, width];
+    y float32 or bfloat16, weight and bias float32.  With ``cast_to`` the new x is also returned rounded once to that
+    dtype (float32: x itself is returned)."""
+    _cuda(x, y, weight, bias)
+    _contig(x, y, weight, bias)
+    _f32(x, weight, bias)
+    tokens, width = x.shape
+    if tuple(y.shape) != (tokens, width) or weight.numel() != width or (bias is not None and bias.numel() != width):
+        raise KernelError("norm_add: y, the weight or the bias do not fit the stream")
+    out = None
+    if cast_to is not None and cast_to != torch.float32:
+        out = torch.empty((tokens, width), dtype=cast_to, device=x.device)
+    rc = load_cuda_library("post_norm.cu").b200_norm_add(
+        _p(x), _p(y), _code(y), _p(bias), _p(weight), ctypes.c_float(eps), _p(out),
+        _code(out) if out is not None else F32, tokens, width, _stream())
+    _ok(rc, "norm_add")
+    if cast_to is None:
+        return None
+    return out if out is not None else x
+
+
+def norm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+              rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[r] = x[rows[r]] / sqrt(mean(x[rows[r]]^2) + eps) * weight for the float32 stream x (every row without
+    ``rows``), rounded once to ``out_dtype``."""
+    _cuda(x, weight, rows)
+    _contig(x, weight, rows)
+    _f32(x, weight)
+    _i32(rows)
+    width = x.shape[1]
+    if weight.numel() != width:
+        raise KernelError("norm_rows: one weight per column is needed")
+    n = x.shape[0] if rows is None else rows.numel()
+    out = torch.empty((n, width), dtype=out_dtype, device=x.device)
+    rc = load_cuda_library("post_norm.cu").b200_norm_rows(_p(out), _code(out), _p(x), _p(rows), _p(weight),
+                                                          ctypes.c_float(eps), n, width, _stream())
+    _ok(rc, "norm_rows")
     return out

@@ -277,14 +277,20 @@ class GroupedAttention(Part):
     """Grouped-query softmax attention over the paged cache with keys ``head_dim`` wide and values ``v_head_dim``
     wide, from one packed projection (q rows, k rows, v rows, then gate rows if gated).  Each of these is a
     parameter of the part and may be absent:
-      * ``bias``: q, k and v have biases (one packed vector, added in float before anything else);
-      * ``qk_norm_eps``: q and k are RMS-normed per head with one weight vector each (``q_norm``, ``k_norm``);
+      * ``bias``: q, k and v have biases (one packed vector, added in float before anything else);  ``out_bias``: so
+        has the output projection (``o_bias``; a block that adds the mixer's output through a kernel of its own may
+        take the bias into that kernel, ``defer_output_bias``);
+      * ``qk_norm_eps``: q and k are RMS-normed, ``qk_norm_scope`` "head": per head with one weight vector each
+        (``q_norm``, ``k_norm`` of a head's size), "projection": over all of a token's q columns at once, before they
+        are split into heads, and over all of its k columns (weights of the projections' sizes);
       * ``position_encoding`` / ``rot_dims``: the first rot_dims coordinates of every q and k head are rotated
         (the encoding says whether pairs are interleaved or half-split);
       * ``window`` W: a query at position p reads keys p - W < j <= p;  ``chunk`` C: only keys from p - p % C on
         (its own block of C positions, blocks counted from the sequence's start); both masks may be set;
       * ``sink``: a learned number per head whose exponential joins the softmax's denominator (no key, no value,
-        not scaled);
+        not scaled); "zero": the number is 0 for every head and no parameter (one is added to the denominator);
+      * ``own_kv`` False: the layer has no key and value projections (the packed matrix and bias hold q alone) and
+        reads the cache of the run-list entry that its own entry names, with its own queries, masks and scale;
       * ``gate``: the heads' outputs are multiplied by sigmoid(g) before the output projection.
     Softmax weights stay floats."""
     category = "mixer"
@@ -301,36 +307,57 @@ class GroupedAttention(Part):
         self.window = spec.get("window")
         self.chunk = spec.get("chunk")
         self.scale = float(spec.get("softmax_scale", 1.0 / math.sqrt(self.d)))
-        self.sink = bool(spec.get("sink", False))
+        self.zero_sink = spec.get("sink") == "zero"
+        self.sink = bool(spec.get("sink", False)) and not self.zero_sink
         self.gate = bool(spec.get("gate", False))
+        self.out_bias = bool(spec.get("out_bias", False))
+        self.norm_scope = str(spec.get("qk_norm_scope", "head"))
+        self.own_kv = bool(spec.get("own_kv", True))
+        if self.norm_scope not in ("head", "projection"):
+            raise ValueError(f"qk_norm_scope {self.norm_scope!r} is refused: head or projection")
         if self.nh % self.nkv:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         for width in (self.d, self.dv):
             if width % 2 or not 2 <= width <= 512:
                 raise ValueError(f"head size {width} is refused: the attention kernels take even head sizes up to 512")
+        if not self.own_kv and (self.gate or self.norm_scope != "projection"):
+            raise ValueError("a layer without keys of its own is served with projection-wide norms and no gate")
         name = spec.get("position_encoding")
         self.rope = env.position_encodings[name] if name else None
         self.rot_dims = int(spec.get("rot_dims") or (self.rope.rot_dim if self.rope else 0))
         if self.rope is not None and (self.rot_dims != self.rope.rot_dim or self.rot_dims > self.d):
             raise ValueError("the rotation does not fit the head or the encoding")
-        self.qkv_channels = (self.nh + self.nkv) * self.d + self.nkv * self.dv
+        self.q_channels = self.nh * self.d
+        self.qkv_channels = self.q_channels + (self.nkv * (self.d + self.dv) if self.own_kv else 0)
+        self.bias_deferred = False
+        self.zero_sinks = torch.zeros(self.nh, dtype=torch.float32, device=env.device) if self.zero_sink else None
 
     def param_decls(self):
         rows = self.qkv_channels + (self.nh * self.dv if self.gate else 0)
         decls = {"qkv_proj": ParamDecl((rows, self.hidden)), "o_proj": ParamDecl((self.hidden, self.nh * self.dv))}
         if self.bias:
             decls["qkv_bias"] = ParamDecl((self.qkv_channels,), "vector")
+        if self.out_bias:
+            decls["o_bias"] = ParamDecl((self.hidden,), "vector")
         if self.qk_eps is not None:
-            decls["q_norm"] = ParamDecl((self.d,), "vector")
-            decls["k_norm"] = ParamDecl((self.d,), "vector")
+            joint = self.norm_scope == "projection"
+            decls["q_norm"] = ParamDecl((self.q_channels if joint else self.d,), "vector")
+            if self.own_kv:
+                decls["k_norm"] = ParamDecl((self.nkv * self.d if joint else self.d,), "vector")
         if self.sink:
             decls["sink"] = ParamDecl((self.nh,), "vector")
         return decls
 
     def bind(self, name, tensor):
         super().bind(name, tensor)
-        if name in ("qkv_bias", "q_norm", "k_norm", "sink"):
+        if name in ("qkv_bias", "q_norm", "k_norm", "sink", "o_bias"):
             self.params[name] = tensor.to(torch.float32).contiguous()
+
+    def defer_output_bias(self) -> bool:
+        """Asked by a block whose next kernel can add the output projection's bias (``params["o_bias"]``) in float:
+        True if there is one, and from then on ``forward`` returns the projection without it."""
+        self.bias_deferred = self.out_bias
+        return self.bias_deferred
 
     def cache_spec(self):
         # a chunk's earlier blocks are never read again, but their pages are kept: only a window gives pages back
@@ -346,16 +373,24 @@ class GroupedAttention(Part):
         packed = ops.linear(x, p["qkv_proj"])
         q = torch.empty((tokens, self.nh * self.d), dtype=packed.dtype, device=packed.device)
         slots = ctx.slots[cache.group] if cache.writes else None
-        ops.heads_prepare(packed, q, cache.k, cache.v, ctx.positions, slots, self.nh, self.nkv, self.d, self.dv,
-                          bias=p.get("qkv_bias"), q_weight=p.get("q_norm"), k_weight=p.get("k_norm"),
-                          eps=float(self.qk_eps or 0.0), inv_freq=rope.inv_freq if rope else None,
-                          rot_dims=self.rot_dims if rope else 0,
-                          interleaved=getattr(rope, "pairing", "half_split") == "interleaved")
+        if cache.writes and not self.own_kv:
+            raise RuntimeError("a layer without keys of its own must read the cache of another run-list entry")
+        prepare = ops.joint_heads_prepare if self.norm_scope == "projection" else ops.heads_prepare
+        extra = {"has_kv": self.own_kv} if self.norm_scope == "projection" else {}
+        prepare(packed, q, cache.k, cache.v, ctx.positions, slots, self.nh, self.nkv, self.d, self.dv,
+                bias=p.get("qkv_bias"), q_weight=p.get("q_norm"), k_weight=p.get("k_norm"),
+                eps=float(self.qk_eps or 0.0), inv_freq=rope.inv_freq if rope else None,
+                rot_dims=self.rot_dims if rope else 0,
+                interleaved=getattr(rope, "pairing", "half_split") == "interleaved", **extra)
         out = torch.empty((tokens, self.nh * self.dv), dtype=packed.dtype, device=packed.device)
-        _masked_attention(self, q, out, ctx, cache, self.nh, self.nkv, self.d, self.dv, p.get("sink"))
+        _masked_attention(self, q, out, ctx, cache, self.nh, self.nkv, self.d, self.dv,
+                          self.zero_sinks if self.zero_sink else p.get("sink"))
         if self.gate:
             ops.sigmoid_gate_mul(out, packed, self.qkv_channels)
-        return ops.linear(out, p["o_proj"])
+        y = ops.linear(out, p["o_proj"])
+        if self.out_bias and not self.bias_deferred:
+            ops.add_row_bias(y, p["o_bias"])
+        return y
 
 
 class LatentAttention(Part):

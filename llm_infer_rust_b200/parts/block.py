@@ -205,7 +205,55 @@ class MultiStreamPreNorm:
         return y, carry
 
 
+class PostNormStream:
+    """A layer whose norms sit on the sublayers' outputs, over a float32 stream x; the sublayers read x itself:
+
+        x <- x + norm_m(mixer(x));    x <- x + norm_f(feed_forward(x));    x <- x + token_side(x, token ids)
+
+    Parts by name: ``mixer`` and ``mixer_norm``; all or none of ``feed_forward`` and ``ff_norm``; optionally
+    ``token_side`` (a per-layer read of a second token table that brings its own norm).  The norms are
+    ``output_rms_norm``: each add is one kernel that also hands on the new x rounded to the engine's dtype, which the
+    next sublayer's products read (the block passes it on as ``residual``; the stream itself is ``h``).  A mixer that
+    has an output bias and offers ``defer_output_bias()`` leaves the bias to that kernel.  A feed-forward that says
+    ``needs_context`` is also given the step's context."""
+    category = "block"
+
+    def __init__(self, layer_spec, env):
+        self.spec = layer_spec
+        self.env = env
+        parts = layer_spec.parts
+        self.mixer = build_part("mixer", layer_spec["mixer"], env)
+        self.mixer_norm = build_part("norm", layer_spec["mixer_norm"], env)
+        self.feed_forward = build_part("feed_forward", parts["feed_forward"], env) if "feed_forward" in parts else None
+        self.ff_norm = build_part("norm", layer_spec["ff_norm"], env) if self.feed_forward is not None else None
+        self.token_side = build_part("token_side", parts["token_side"], env) if "token_side" in parts else None
+        for norm in (self.mixer_norm, self.ff_norm):
+            if norm is not None and not hasattr(norm, "add_into"):
+                raise ValueError("this block needs norms that add into the stream (output_rms_norm)")
+        defer = getattr(self.mixer, "defer_output_bias", None)
+        self.mixer_bias_here = bool(defer()) if defer is not None else False
+
+    def children(self):
+        named = {"mixer": self.mixer, "mixer_norm": self.mixer_norm, "feed_forward": self.feed_forward,
+                 "ff_norm": self.ff_norm, "token_side": self.token_side}
+        return {name: part for name, part in named.items() if part is not None}
+
+    def forward(self, h, residual, ctx, cache):
+        ops.flush_chain()
+        x = ops.cast(h, self.env.dtype) if residual is None else residual
+        y = self.mixer.forward(x, ctx, cache)
+        x = self.mixer_norm.add_into(h, y, bias=self.mixer.params.get("o_bias") if self.mixer_bias_here else None)
+        if self.feed_forward is not None:
+            y = self.feed_forward.forward(x, ctx) if getattr(self.feed_forward, "needs_context", False) \
+                else self.feed_forward.forward(x)
+            x = self.ff_norm.add_into(h, y)
+        if self.token_side is not None:
+            x = self.token_side.add_into(h, x, ctx)
+        return h, x
+
+
 register_part("stream_mix", "stream_mix", StreamMix)
+register_part("block", "post_norm_stream", PostNormStream)
 register_part("block", "pre_norm_deferred_add", PreNormDeferredAdd)
 register_part("block", "multi_stream_pre_norm", MultiStreamPreNorm)
 register_part("block", "pre_norm_input_conv", PreNormInputConv)

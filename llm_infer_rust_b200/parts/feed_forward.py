@@ -70,8 +70,8 @@ class PolyNormFF(Part):
 
 
 class DenseActFF(Part):
-    """down(act(up(x))), no gate and no bias; ``activation``: gelu_erf (the exact gelu), gelu_tanh or silu,
-    computed in float on the rounded projection and rounded once."""
+    """down(act(up(x))), no gate and no bias; ``activation``: gelu_erf (the exact gelu), gelu_tanh, silu or
+    relu_squared (max(z, 0)^2), computed in float on the rounded projection and rounded once."""
     category = "feed_forward"
 
     def __init__(self, spec, env):
@@ -123,7 +123,69 @@ class TableExperts(Part):
                                  p["down_proj"].view(self.experts, self.hidden, self.inter))
 
 
+class RoutedExperts(Part):
+    """A mixture of gated experts chosen by a router, with an optional shared expert that every token takes:
+
+        z = router x (in float);  s = softmax(z) over all experts (``scores`` "sigmoid": a sigmoid of each)
+        experts form ``groups`` equal groups of neighbours; a group's score is its largest s; only experts of the
+        ``keep_groups`` best groups can be chosen; the ``top`` largest of those are, with weights s (divided by their
+        sum if ``renormalize``)
+        y = sum_k s_k down[e_k] glu(gate[e_k] x, up[e_k] x)  +  shared_down glu(shared_gate x, shared_up x)
+
+    ``activation``: "swiglu" (silu(g) u) or "clamped_swish_glu" (g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit),
+    u' = clamp(u, -limit, limit); ``alpha`` 1.702 unless given; the shared expert has its own ``shared_limit``).
+    ``gate_up_proj`` [experts * 2 ff, hidden] holds expert after expert, each its gate rows and then its up rows;
+    ``down_proj`` [experts * hidden, ff]; the shared expert's ``shared_gate_up_proj`` [2 sff, hidden] and
+    ``shared_down_proj`` [hidden, sff] exist if ``shared_intermediate_size`` > 0.  No biases.  The output is float32
+    (the weighted sum and the shared expert's share are added in float)."""
+    category = "feed_forward"
+    _GLU = {"swiglu": "silu", "clamped_swish_glu": "clamped_swish"}
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = int(spec["hidden_size"])
+        self.inter = int(spec["intermediate_size"])
+        self.experts = int(spec["experts"])
+        self.top = int(spec["top"])
+        self.groups = int(spec.get("groups") or 1)
+        self.keep = int(spec.get("keep_groups") or self.groups)
+        self.scores = str(spec.get("scores", "softmax"))
+        self.renormalize = bool(spec.get("renormalize", False))
+        self.activation = str(spec.get("activation", "swiglu"))
+        self.limit = float(spec.get("limit") or 0.0)
+        self.alpha = float(spec.get("alpha") or 1.702)
+        self.shared_inter = int(spec.get("shared_intermediate_size") or 0)
+        self.shared_limit = float(spec.get("shared_limit") or 0.0)
+        if self.activation not in self._GLU:
+            raise ValueError(f"activation {self.activation!r} is refused: {sorted(self._GLU)}")
+        if self.experts % self.groups or not 1 <= self.keep <= self.groups or \
+                not 1 <= self.top <= self.keep * (self.experts // self.groups):
+            raise ValueError("groups must divide the experts, and top experts must fit the groups that are kept")
+
+    def param_decls(self):
+        decls = {"router": ParamDecl((self.experts, self.hidden)),
+                 "gate_up_proj": ParamDecl((self.experts * 2 * self.inter, self.hidden)),
+                 "down_proj": ParamDecl((self.experts * self.hidden, self.inter))}
+        if self.shared_inter:
+            decls["shared_gate_up_proj"] = ParamDecl((2 * self.shared_inter, self.hidden))
+            decls["shared_down_proj"] = ParamDecl((self.hidden, self.shared_inter))
+        return decls
+
+    def forward(self, x):
+        p = self.params
+        glu = self._GLU[self.activation]
+        choice, gains = ops.expert_router(x, p["router"], self.top, self.groups, self.keep, self.scores, self.renormalize)
+        shared = None
+        if self.shared_inter:
+            a = ops.glu_columns(ops.linear(x, p["shared_gate_up_proj"]), glu, self.shared_limit, self.alpha)
+            shared = ops.linear(a, p["shared_down_proj"])
+        return ops.routed_experts(x, choice, gains, p["gate_up_proj"].view(self.experts, 2 * self.inter, self.hidden),
+                                  p["down_proj"].view(self.experts, self.hidden, self.inter), glu, self.limit,
+                                  self.alpha, add=shared)
+
+
 register_part("feed_forward", "swiglu", SwiGLU)
+register_part("feed_forward", "routed_experts", RoutedExperts)
 register_part("feed_forward", "dense_act", DenseActFF)
 register_part("feed_forward", "table_experts", TableExperts)
 register_part("feed_forward", "poly_norm", PolyNormFF)

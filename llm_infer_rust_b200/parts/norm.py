@@ -137,6 +137,41 @@ class StreamRMSNorm(Part):
         return self.read(x, residual, None, rows=rows, store=write_residual)
 
 
+class OutputRMSNorm(Part):
+    """RMS norm on a sublayer's OUTPUT, for a residual stream that is float32 whatever the engine's dtype:
+
+        ``add_into(stream, y)``:  stream <- stream + (y + bias) / sqrt(mean((y + bias)^2) + eps) * weight
+
+    in float and in place, one kernel; it returns the new stream rounded once to the engine's dtype (the stream itself
+    in a float32 engine), which is what the next sublayer's first product reads.  ``bias`` (float32, per column) is an
+    output projection's bias that its owner left to this kernel.  ``forward`` / ``forward_add`` are the plain norm of
+    the stream itself at chosen rows (a model's last norm); ``forward_add`` is handed the rounded copy that the blocks
+    pass on as ``residual`` and does not need it."""
+    category = "norm"
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.width = int(spec["width"])
+        self.eps = float(spec["eps"])
+
+    def param_decls(self):
+        return {"weight": ParamDecl((self.width,), "vector")}
+
+    def bind(self, name, tensor):
+        super().bind(name, tensor)
+        self.params[name] = tensor.to(torch.float32).contiguous()
+
+    def add_into(self, stream, y, bias=None):
+        return ops.norm_add(stream, y, self.params["weight"], self.eps, bias=bias, cast_to=self.env.dtype)
+
+    def forward(self, x, out=None, rows=None):
+        return ops.norm_rows(x, self.params["weight"], self.eps, self.env.dtype, rows=rows)
+
+    def forward_add(self, x, residual, out=None, rows=None, write_residual=True):
+        return ops.norm_rows(x, self.params["weight"], self.eps, self.env.dtype, rows=rows)
+
+
 register_part("norm", "rms_norm", RMSNorm)
+register_part("norm", "output_rms_norm", OutputRMSNorm)
 register_part("norm", "stream_rms_norm", StreamRMSNorm)
 register_part("norm", "scalar_rms_norm", ScalarRMSNorm)

@@ -4,7 +4,7 @@ from __future__ import annotations
 from typing import Callable, Dict
 
 CATEGORIES = ("norm", "position_encoding", "mixer", "feed_forward", "block", "embedding", "head", "token_conv",
-              "stream_mix")
+              "stream_mix", "token_side")
 _PARTS: Dict[str, Dict[str, Callable]] = {c: {} for c in CATEGORIES}
 
 

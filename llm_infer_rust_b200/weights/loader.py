@@ -136,7 +136,7 @@ def load_weights(model, plan: Sequence[WeightBinding], model_dir: str,
         check_checkpoint(ckpt, plan, model_dir)
         deferred = []
         for binding in plan:
-            if binding.optional and not all(s.name in ckpt for s in binding.sources):
+            if binding.optional and (not binding.sources or not all(s.name in ckpt for s in binding.sources)):
                 if binding.alias_of is None:
                     continue
                 deferred.append(binding)
