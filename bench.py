@@ -34,6 +34,11 @@ kernel of Qwen3's path, each with its share of its roofline (``--design-sizes``,
 ``--design mukenex`` does the same for Mukenex (latent attention over a window with sinks, grouped attention over
 blocks of positions, lightning retention, experts chosen by a table, a residual of four streams).
 
+``--design torinex`` does the same for Torinex (attention over blocks of positions with projection-wide norms and one
+added to the softmax's denominator, layers that read another layer's keys and values, routed experts with groups and
+a shared expert, a per-layer token input, norms on the sublayers' outputs over a float32 stream); its routed experts
+also stand beside Mukenex's.
+
 Peaks come from MEASURED_PEAKS.json beside this file when it is there.  Weights are random
 (drawn on the device), token ids are synthetic.  One GPU only.
 """
@@ -668,7 +673,182 @@ def mukenex_kernel_table(size, peak):
     return out
 
 
-DESIGNS = {"kefetar": (kefetar_config, kernel_table), "mukenex": (mukenex_config, mukenex_kernel_table)}
+# ----------------------------------------------------------------------------- --design torinex
+TORINEX_EXPERTS = dict(experts=16, top=4, groups=4, keep=2)
+
+
+def torinex_config(size, layers):
+    """Attention layers over blocks of 1,024 positions; every second layer reads the keys and values of the layer
+    before it; dense feed-forwards of 1.5 x Qwen3's intermediate size (two matrices with the parameters of Qwen3's
+    three) in turn with 16 routed experts (4 a token out of 2 of 4 groups) and a shared expert which together take a
+    token through as many parameters as Qwen3's feed-forward; a per-layer token input 64 wide."""
+    z = DESIGN_SIZES[size]
+    I = z["inter"]
+
+    def layer(i):
+        mixer = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["head_dim"], "vdim": z["head_dim"],
+                 "scale": z["head_dim"] ** -0.5, "mask": {"size": 1024}, "rot": {"base": 1e6, "dims": z["head_dim"]}}
+        if i % 2 == 1:
+            mixer["kv_from"] = i - 1
+        r = TORINEX_EXPERTS
+        mlp = {"kind": "dense", "ff": I * 3 // 2} if i % 2 == 0 else {
+            "kind": "moe", "expert": {"ff": I // 8, "limit": 7.0}, "shared": {"ff": I // 2, "limit": 7.0},
+            "router": {"experts": r["experts"], "top": r["top"], "groups": {"count": r["groups"], "keep": r["keep"]}}}
+        return {"type": "attention", "mixer": mixer, "mlp": mlp}
+
+    return {"architecture": "Torinex", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
+            "token_side": {"dim": 64}, "layers": [layer(i) for i in range(layers)]}
+
+
+def torinex_kernel_table(size, peak):
+    """Every kernel of Torinex alone, beside the like kernel of Qwen3's path (and of Mukenex's experts, the closest
+    routed feed-forward), at one layer's sizes: a prompt portion of 2,048 tokens and a decode step of 8 rows at 2,048
+    tokens (``frac`` as in ``kernel_table``)."""
+    import types
+    import torch
+    from llm_infer_rust_b200.kernels import ops
+    from llm_infer_rust_b200.parts.attention import decode_splits
+    z = DESIGN_SIZES[size]
+    W, nh, nkv, d, I = z["width"], z["heads"], z["kv_heads"], z["head_dim"], z["inter"]
+    r = TORINEX_EXPERTS
+    E, top, groups, keep, ffe, side, block = r["experts"], r["top"], r["groups"], r["keep"], I // 8, 64, 1024
+    dev, bf = torch.device("cuda"), torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    page, ctx_len, rows_dec = 16, 2048, 8
+    out = {}
+
+    def put(name, us, nbytes=None, flops=None, of="hbm"):
+        rec = {"us": round(us, 2)}
+        if nbytes is not None:
+            rec["gb_s"] = round(nbytes / us / 1e3, 1)
+            rec["frac"] = round(nbytes / us / 1e3 / peak["hbm_gbs"], 3)
+        if flops is not None:
+            rec["tflops"] = round(flops / us / 1e6, 2)
+            rec["frac"] = round(flops / us / 1e6 / peak["bf16_tflops"], 3)
+            rec["of"] = of
+        out[name] = rec
+
+    def step(rows):
+        cu, pos = [0], []
+        for prefix, n in rows:
+            cu.append(cu[-1] + n)
+            pos += list(range(prefix, prefix + n))
+        R = len(rows)
+        width = -(-max(p + n for p, n in rows) // page)
+        table = torch.arange(1, R * width + 1, dtype=torch.int32, device=dev).view(R, width).contiguous()
+        slots = [int(table[r_, (p + i) // page]) * page + (p + i) % page for r_, (p, n) in enumerate(rows) for i in range(n)]
+        return types.SimpleNamespace(
+            num_rows=R, cu_q=i32(cu), positions=i32(pos), prefix_len=i32([p for p, _ in rows]),
+            kv_len=i32([p + n for p, n in rows]), slots=i32(slots), table=table, rows=i32(list(range(R))),
+            tokens=cu[-1], pages=R * width + 1)
+
+    for phase, c in (("prefill", step([(0, ctx_len)])), ("decode", step([(ctx_len - 1, 1)] * rows_dec))):
+        T = c.tokens
+        # --- the residual: a sublayer's output normed and added into the float stream, rounded for the next product
+        stream = torch.randn(T, W, device=dev)
+        y = torch.randn(T, W, device=dev).to(bf)
+        wn, ob = torch.ones(W, device=dev), torch.zeros(W, device=dev)
+        put(f"{phase}.torinex.norm_add", timed_alone(lambda: ops.norm_add(stream, y, wn, 1e-5, bias=ob, cast_to=bf), flush),
+            T * W * 12)
+        res_b, xb = torch.randn(T, W, device=dev).to(bf), torch.randn(T, W, device=dev).to(bf)
+        wb = torch.ones(W, dtype=bf, device=dev)
+        put(f"{phase}.qwen3.add_rms_norm", timed_alone(lambda: ops.add_rms_norm(xb, res_b, wb, 1e-6), flush), T * W * 8)
+        # --- between the projection and attention: bias, one norm over all of q and one over all of k, rotation, store
+        cq = (nh + 2 * nkv) * d
+        packed = (torch.randn(T, cq, device=dev) * 0.5).to(bf)
+        k_cache = torch.zeros(c.pages, nkv, page, d, dtype=bf, device=dev).normal_()
+        v_cache = torch.zeros(c.pages, nkv, page, d, dtype=bf, device=dev).normal_()
+        q = torch.empty(T, nh * d, dtype=bf, device=dev)
+        bias, qw, kw = torch.zeros(cq, device=dev), torch.ones(nh * d, device=dev), torch.ones(nkv * d, device=dev)
+        inv_freq = torch.pow(torch.tensor(1e6), -torch.arange(0, d, 2) / d).to(dev)
+        put(f"{phase}.torinex.joint_heads_prepare", timed_alone(lambda: ops.joint_heads_prepare(
+            packed, q, k_cache, v_cache, c.positions, c.slots, nh, nkv, d, d, bias=bias, q_weight=qw, k_weight=kw,
+            eps=1e-5, inv_freq=inv_freq, rot_dims=d, interleaved=True), flush), T * cq * 4)
+        q_only = packed[:, :nh * d].contiguous()
+        put(f"{phase}.torinex.joint_heads_prepare_q", timed_alone(lambda: ops.joint_heads_prepare(
+            q_only, q, None, None, c.positions, None, nh, nkv, d, d, bias=bias[:nh * d], q_weight=qw, k_weight=None,
+            eps=1e-5, inv_freq=inv_freq, rot_dims=d, interleaved=True, has_kv=False), flush), T * nh * d * 4)
+        cos, sin = torch.ones(4096, d // 2, device=dev), torch.zeros(4096, d // 2, device=dev)
+        hn = torch.ones(d, dtype=bf, device=dev)
+        put(f"{phase}.qwen3.qkv_post", timed_alone(lambda: ops.qkv_post(
+            packed, q, k_cache, v_cache, hn, hn, 1e-6, cos, sin, d, c.positions, c.slots, nh, nkv, d), flush), T * cq * 4)
+        # --- attention over blocks of positions with one added to the denominator
+        o = torch.empty(T, nh * d, dtype=bf, device=dev)
+        sinks = torch.zeros(nh, device=dev)
+        if phase == "prefill":
+            pairs_seen = sum(p % block + 1 for p in range(T))
+            put("prefill.torinex.attention_blocks_sink", timed_alone(lambda: ops.prefill_attention(
+                q, k_cache, v_cache, o, c.table, c.cu_q, c.kv_len, c.prefix_len, c.rows, 1, T, nh, nkv, d, page, None,
+                d ** -0.5, v_head_dim=d, precise_weights=True, chunk=block, sinks=sinks), flush, repeats=3),
+                flops=4.0 * nh * d * pairs_seen, of="bf16")
+            put("prefill.qwen3.attention", timed_alone(lambda: ops.prefill_attention(
+                q, k_cache, v_cache, o, c.table, c.cu_q, c.kv_len, c.prefix_len, c.rows, 1, T, nh, nkv, d, page, None,
+                d ** -0.5), flush), flops=4.0 * nh * d * T * (T + 1) / 2, of="bf16")
+        else:
+            def decode(name, bound, nbytes, **kw):
+                per_split = ops.decode_ctas_per_split(bf, rows_dec, nh, nkv, d, page, True)
+                splits = decode_splits(per_split, bound, 148)
+                need = ops.decode_scratch_floats(rows_dec, nh, d, splits)
+                scratch = torch.empty(max(need, 1), device=dev)
+                put(name, timed_alone(lambda: ops.decode_attention(
+                    q, k_cache, v_cache, o, scratch, c.table, c.cu_q, c.kv_len, c.rows, rows_dec, nh, nkv, d, page,
+                    None, d ** -0.5, splits, **kw), flush), nbytes)
+            decode("decode.torinex.attention_blocks_sink", block, rows_dec * block * nkv * d * 2 * 2,
+                   v_head_dim=d, precise_weights=True, chunk=block, sinks=sinks)
+            decode("decode.qwen3.attention", ctx_len, rows_dec * ctx_len * nkv * d * 2 * 2)
+        # --- activations
+        zf = torch.randn(T, I * 3 // 2, device=dev).to(bf)
+        put(f"{phase}.torinex.relu_squared", timed_alone(lambda: ops.activate(zf, "relu_squared", in_place=True), flush),
+            T * I * 3 // 2 * 4)
+        gs = torch.randn(T, I, device=dev).to(bf)                   # the shared expert's gate and up columns
+        put(f"{phase}.torinex.glu_clamped_swish", timed_alone(lambda: ops.glu_columns(gs, "clamped_swish", 7.0, 1.702), flush),
+            T * I // 2 * 6)
+        gu = torch.randn(T, 2 * I, device=dev).to(bf)
+        put(f"{phase}.qwen3.silu_mul", timed_alone(lambda: ops.silu_mul(gu), flush), T * I * 6)
+        # --- the per-layer token input: the gate on a row of the second table
+        zs = torch.randn(T, side, device=dev).to(bf)
+        table2 = torch.randn(4096, 8 * side, device=dev).to(bf)
+        ids = torch.randint(0, 4096, (T,), device=dev, dtype=torch.int32)
+        put(f"{phase}.torinex.act_table_mul", timed_alone(lambda: ops.act_table_mul(zs, "gelu_tanh", table2, ids, 3 * side),
+                                                          flush), T * side * 6)
+        # --- router and experts beside Mukenex's experts and Qwen3's feed-forward with the same active parameters
+        xe = torch.randn(T, W, device=dev).to(bf)
+        wr = (torch.randn(E, W, device=dev) * W ** -0.5).to(bf)
+        put(f"{phase}.torinex.expert_router", timed_alone(lambda: ops.expert_router(xe, wr, top, groups, keep), flush),
+            T * W * 2 + E * W * 2 + T * top * 8)
+        choice, gains = ops.expert_router(xe, wr, top, groups, keep)
+        gate_up = (torch.randn(E, 2 * ffe, W, device=dev) * W ** -0.5).to(bf)
+        down = (torch.randn(E, W, ffe, device=dev) * ffe ** -0.5).to(bf)
+        share = torch.randn(T, W, device=dev).to(bf)
+        us = timed_alone(lambda: ops.routed_experts(xe, choice, gains, gate_up, down, "clamped_swish", 7.0, 1.702,
+                                                    add=share), flush)
+        used = int(torch.unique(choice).numel())
+        if phase == "prefill":
+            put("prefill.torinex.routed_experts", us, flops=6.0 * T * top * W * ffe, of="bf16")
+        else:
+            put("decode.torinex.routed_experts", us, used * 3 * W * ffe * 2)
+        E2, top2, ffe2 = 8, 2, I // 4                               # Mukenex's experts at the same active parameters
+        tbl = torch.stack([torch.randperm(E2)[:top2] for _ in range(4096)]).to(torch.int32).to(dev)
+        gate_up2 = (torch.randn(E2, 2 * ffe2, W, device=dev) * W ** -0.5).to(bf)
+        down2 = (torch.randn(E2, W, ffe2, device=dev) * ffe2 ** -0.5).to(bf)
+        us = timed_alone(lambda: ops.table_experts(xe, ids, tbl, gate_up2, down2), flush)
+        if phase == "prefill":
+            put("prefill.mukenex.table_experts", us, flops=6.0 * T * top2 * W * ffe2, of="bf16")
+        else:
+            put("decode.mukenex.table_experts", us, min(E2, T * top2) * 3 * W * ffe2 * 2)
+        wgu = (torch.randn(2 * I, W, device=dev) * W ** -0.5).to(bf)
+        wdn = (torch.randn(W, I, device=dev) * I ** -0.5).to(bf)
+        us = timed_alone(lambda: ops.linear(ops.silu_mul(ops.linear(xe, wgu)), wdn), flush)
+        if phase == "prefill":
+            put("prefill.qwen3.feed_forward", us, flops=6.0 * T * W * I, of="bf16")
+        else:
+            put("decode.qwen3.feed_forward", us, 3 * W * I * 2)
+    return out
+
+
+DESIGNS = {"kefetar": (kefetar_config, kernel_table), "mukenex": (mukenex_config, mukenex_kernel_table),
+           "torinex": (torinex_config, torinex_kernel_table)}
 
 
 def design_main(args) -> int:
@@ -720,8 +900,8 @@ def main() -> int:
                     help="other shapes measured into `points` (decode at batch 1 / 8 / 64, prefill), comma separated")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one phase alone and print a short line (for profiling)")
-    ap.add_argument("--design", choices=["qwen3", "kefetar", "mukenex"], default="qwen3",
-                    help="kefetar, mukenex: that design beside Qwen3 at equal sizes, and its kernels alone (another line)")
+    ap.add_argument("--design", choices=["qwen3", "kefetar", "mukenex", "torinex"], default="qwen3",
+                    help="kefetar, mukenex, torinex: that design beside Qwen3 at equal sizes, and its kernels alone (another line)")
     ap.add_argument("--design-sizes", default="1k,4k", help="layer sizes of --design kefetar / mukenex, comma separated")
     ap.add_argument("--no-kernels", action="store_true", help="--design ... without the table of single kernels")
     args = ap.parse_args()

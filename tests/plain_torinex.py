@@ -36,14 +36,16 @@ def sigmoid(z: torch.Tensor) -> torch.Tensor:
     return 1.0 / (1.0 + torch.exp(-z))
 
 
-def rotate_pairs(x: torch.Tensor, base: float, dims: int, first_position: int = 0) -> torch.Tensor:
+def rotate_pairs(x: torch.Tensor, base: float, dims: int, first_position: int = 0,
+                 angle_dtype: torch.dtype = torch.float64) -> torch.Tensor:
     """x [T, heads, d]: of every head's first ``dims`` coordinates, coordinate 2i is paired with 2i + 1 and the pair
     (u, v) of the token at position p becomes (u cos a - v sin a, v cos a + u sin a), a = p * base^(-2i / dims); the
-    other coordinates pass."""
+    other coordinates pass.  ``angle_dtype`` float32 rounds the frequency and the product p * f to 32 bits as a
+    32-bit implementation does (at position 3000 that moves an angle by 1e-4); cos and sin are exact after that."""
     T = x.shape[0]
     i = torch.arange(dims // 2, dtype=torch.float64)
-    f = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims)
-    a = (first_position + torch.arange(T, dtype=torch.float64))[:, None] * f[None, :]
+    f = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims).to(angle_dtype)
+    a = ((first_position + torch.arange(T, dtype=torch.float64)).to(angle_dtype)[:, None] * f[None, :]).double()
     cos, sin = torch.cos(a).to(x.dtype)[:, None, :], torch.sin(a).to(x.dtype)[:, None, :]
     u, v = x[..., 0:dims:2], x[..., 1:dims:2]
     out = x.clone()
@@ -133,9 +135,30 @@ def route(z: torch.Tensor, top: int, groups: int, keep: int):
     return chosen, s.gather(1, chosen)
 
 
-def experts_ff(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mlp: dict) -> torch.Tensor:
+def route_margin(z: torch.Tensor, top: int, groups: int, keep: int) -> float:
+    """How far the router's choice is from another one, in logits, at its closest token: the gap between the last
+    group kept and the first one left out (by their largest logits), and between the last expert chosen and the first
+    one left out among the experts of the kept groups.  A choice within rounding of another is a close call."""
+    T, E = z.shape
+    per = E // groups
+    best = z.reshape(T, groups, per).max(-1).values.sort(-1, descending=True).values
+    gap = float("inf")
+    if keep < groups:
+        gap = min(gap, float((best[:, keep - 1] - best[:, keep]).min()))
+    chosen_groups = z.reshape(T, groups, per).max(-1).values.topk(keep, -1).indices
+    allowed = torch.zeros(T, groups, dtype=torch.bool).scatter_(1, chosen_groups, True).repeat_interleave(per, 1)
+    ranked = z.masked_fill(~allowed, float("-inf")).sort(-1, descending=True).values
+    if top < keep * per:
+        gap = min(gap, float((ranked[:, top - 1] - ranked[:, top]).min()))
+    return gap
+
+
+def experts_ff(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mlp: dict,
+               margins: Optional[list] = None) -> torch.Tensor:
     r = mlp["router"]
     groups = r.get("groups") or {"count": 1, "keep": 1}
+    if margins is not None:
+        margins.append(route_margin(h @ w[p + "router"].T, r["top"], groups["count"], groups["keep"]))
     chosen, weight = route(h @ w[p + "router"].T, r["top"], groups["count"], groups["keep"])
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
@@ -156,8 +179,9 @@ def token_side(x: torch.Tensor, ids: List[int], w: Dict[str, torch.Tensor], p: s
 
 # ------------------------------------------------------------------------------------------------ the model
 def forward(config: dict, weights: Dict[str, torch.Tensor], ids: List[int], dtype=torch.float64,
-            layers_out: Optional[list] = None) -> torch.Tensor:
-    """Logits [T, vocab] of one whole sequence.  ``layers_out``: a list that receives x after every layer."""
+            layers_out: Optional[list] = None, margins_out: Optional[list] = None) -> torch.Tensor:
+    """Logits [T, vocab] of one whole sequence.  ``layers_out``: a list that receives x after every layer;
+    ``margins_out``: one that receives every router's ``route_margin``."""
     w = {n: (t if not t.is_floating_point() else t.to(dtype)) for n, t in weights.items()}
     eps = config["norm"]["eps"]
     side = config.get("token_side")
@@ -171,7 +195,7 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], ids: List[int], dtyp
         x = x + rms_norm(attention(x, w, p + "mix.", m, eps, k, v), w[p + "norm1"], eps)
         mlp = layer.get("mlp")
         if mlp:
-            y = dense_ff(x, w, p + "mlp.") if mlp["kind"] == "dense" else experts_ff(x, w, p + "mlp.", mlp)
+            y = dense_ff(x, w, p + "mlp.") if mlp["kind"] == "dense" else experts_ff(x, w, p + "mlp.", mlp, margins_out)
             x = x + rms_norm(y, w[p + "norm2"], eps)
         if side:
             x = x + token_side(x, ids, w, p, i, side["dim"], eps)
