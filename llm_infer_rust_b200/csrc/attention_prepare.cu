@@ -163,125 +163,131 @@ latent_prepare_kernel(const T* __restrict__ x, int in_stride, const T* __restric
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 joint_heads_prepare_kernel(const T* __restrict__ x, int in_stride, const float* __restrict__ bias,
                            const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
                            const float* __restrict__ inv_freq, int rot_dims, int interleaved,
                            const int* __restrict__ positions, const int* __restrict__ slots, int nh, int nkv, int d,
                            int dv, int has_kv, int page_size, long long cache_slots, T* __restrict__ q_out,
                            T* __restrict__ k_cache, T* __restrict__ v_cache, int* err) {
-  __shared__ float scratch[33];
-  extern __shared__ float jrow[];                    // q (nh * d), then k (nkv * d), then v (nkv * dv)
+  __shared__ float sums[2][32];
+  extern __shared__ float jrow[];                    // q (nh * d), then k (nkv * d), then v (nkv * dv), then cos, sin
   const int t = blockIdx.x;
   const int nq = nh * d, nk = has_kv ? nkv * d : 0, nv = has_kv ? nkv * dv : 0;
   const T* src = x + static_cast<size_t>(t) * in_stride;
-  float ssq = 0.0f, ssk = 0.0f;
-  for (int i = threadIdx.x; i < nq + nk + nv; i += blockDim.x) {
-    float v = to_f32<T>(src[i]);
-    if (bias != nullptr) v += bias[i];
-    jrow[i] = v;
-    if (i < nq) ssq = fmaf(v, v, ssq);
-    else if (i < nq + nk) ssk = fmaf(v, v, ssk);
-  }
-  ssq = block_sum(ssq, scratch);
-  const float rq = q_w != nullptr ? 1.0f / sqrtf(ssq / static_cast<float>(nq) + eps) : 1.0f;
-  float rk = 1.0f;
-  if (has_kv && k_w != nullptr) {
-    ssk = block_sum(ssk, scratch);
-    rk = 1.0f / sqrtf(ssk / static_cast<float>(nk) + eps);
-  }
-  for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
-    if (i < nq) { if (q_w != nullptr) jrow[i] = jrow[i] * rq * q_w[i]; }
-    else if (k_w != nullptr) jrow[i] = jrow[i] * rk * k_w[i - nq];
-  }
-  __syncthreads();
-  if (inv_freq != nullptr && rot_dims > 0) {
-    const int half = rot_dims >> 1;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  // the token's angles once for all heads (read after the barrier below)
+  const bool rotate = inv_freq != nullptr && rot_dims > 0;
+  const int half = rot_dims >> 1;
+  float* cos_t = jrow + nq + nk + nv;
+  float* sin_t = cos_t + half;
+  if (rotate) {
     const float pos = static_cast<float>(positions[t]);
+    for (int p = threadIdx.x; p < half; p += blockDim.x) sincosf(pos * inv_freq[p], &sin_t[p], &cos_t[p]);
+  }
+  // every size is even: the row is read two columns at a time where it starts on a pair
+  const bool paired = (in_stride & 1) == 0 && (reinterpret_cast<uintptr_t>(x) & (2 * sizeof(T) - 1)) == 0;
+  float ssq = 0.0f, ssk = 0.0f;
+#pragma unroll 4
+  for (int i = 2 * threadIdx.x; i < nq + nk + nv; i += 2 * blockDim.x) {
+    float v0, v1;
+    if (paired) {
+      if constexpr (sizeof(T) == 4) {
+        const float2 p = *reinterpret_cast<const float2*>(src + i);
+        v0 = p.x; v1 = p.y;
+      } else {
+        const uint32_t p = *reinterpret_cast<const uint32_t*>(src + i);
+        v0 = __uint_as_float(p << 16); v1 = __uint_as_float(p & 0xffff0000u);
+      }
+    } else {
+      v0 = to_f32<T>(src[i]); v1 = to_f32<T>(src[i + 1]);
+    }
+    if (bias != nullptr) { v0 += bias[i]; v1 += bias[i + 1]; }
+    jrow[i] = v0;
+    jrow[i + 1] = v1;
+    const float sq = fmaf(v1, v1, v0 * v0);
+    if (i < nq) ssq += sq;
+    else if (i < nq + nk) ssk += sq;
+  }
+  // both sums of squares through one pair of barriers; the additions' order is fixed by the thread layout
+  ssq = warp_sum(ssq);
+  ssk = warp_sum(ssk);
+  if (lane == 0) { sums[0][warp] = ssq; sums[1][warp] = ssk; }
+  __syncthreads();
+  ssq = ssk = 0.0f;
+  for (int w = 0; w < warps; ++w) { ssq += sums[0][w]; ssk += sums[1][w]; }
+  const float rq = q_w != nullptr ? 1.0f / sqrtf(ssq / static_cast<float>(nq) + eps) : 1.0f;
+  const float rk = (has_kv && k_w != nullptr) ? 1.0f / sqrtf(ssk / static_cast<float>(nk) + eps) : 1.0f;
+  if (rotate && !interleaved) {
+    // pairs (p, p + half) lie apart: norm in place, then the rotation, then the stores below read the row
+    for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
+      if (i < nq) { if (q_w != nullptr) jrow[i] = jrow[i] * rq * q_w[i]; }
+      else if (k_w != nullptr) jrow[i] = jrow[i] * rk * k_w[i - nq];
+    }
+    __syncthreads();
     for (int i = threadIdx.x; i < (nh + (has_kv ? nkv : 0)) * half; i += blockDim.x) {
       const int h = i / half, p = i - h * half;
       float* row = jrow + h * d;                    // q heads, then k heads: all d wide and contiguous
-      const int a = interleaved ? 2 * p : p, b = interleaved ? 2 * p + 1 : p + half;
-      float sn, cs;
-      sincosf(pos * inv_freq[p], &sn, &cs);
-      const float u = row[a], v = row[b];
-      row[a] = u * cs - v * sn;
-      row[b] = v * cs + u * sn;
+      const float sn = sin_t[p], cs = cos_t[p];
+      const float u = row[p], v = row[p + half];
+      row[p] = u * cs - v * sn;
+      row[p + half] = v * cs + u * sn;
     }
     __syncthreads();
   }
-  T* qd = q_out + static_cast<size_t>(t) * nq;
-  for (int i = threadIdx.x; i < nq; i += blockDim.x) qd[i] = from_f32<T>(jrow[i]);
-  if (!has_kv || slots == nullptr) return;
-  const int slot = slots[t];
-  if (slot == 0) return;
-  if (slot < 0 || slot >= cache_slots) {
-    if (threadIdx.x == 0) atomicOr(err, B200_ERR_SLOT_RANGE);
-    return;
+  const bool finish = !(rotate && !interleaved);    // norm and rotation of a neighbouring pair happen on the way out
+  int slot = 0;
+  if (has_kv && slots != nullptr) {
+    slot = slots[t];
+    if (slot < 0 || slot >= cache_slots) {
+      if (threadIdx.x == 0) atomicOr(err, B200_ERR_SLOT_RANGE);
+      slot = 0;
+    }
   }
   const int page = slot / page_size, offset = slot - page * page_size;
-  for (int i = threadIdx.x; i < nk; i += blockDim.x) {
-    const int kvh = i / d, c = i - kvh * d;
-    k_cache[((static_cast<size_t>(page) * nkv + kvh) * page_size + offset) * d + c] = from_f32<T>(jrow[nq + i]);
-  }
-  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
-    const int kvh = i / dv, c = i - kvh * dv;
-    v_cache[((static_cast<size_t>(page) * nkv + kvh) * page_size + offset) * dv + c] = from_f32<T>(jrow[nq + nk + i]);
+  T* qd = q_out + static_cast<size_t>(t) * nq;
+#pragma unroll 2
+  for (int i = 2 * threadIdx.x; i < nq + nk + nv; i += 2 * blockDim.x) {
+    float v0 = jrow[i], v1 = jrow[i + 1];           // this thread's own pair in the interleaved form
+    T* dst;
+    if (i < nq + nk) {
+      const bool is_q = i < nq;
+      const int j = is_q ? i : i - nq;               // column within q or within k
+      const int c = j % d;                           // column within the head
+      if (finish) {
+        const float* w = is_q ? q_w : k_w;
+        if (w != nullptr) {
+          const float r = is_q ? rq : rk;
+          v0 = v0 * r * w[j];
+          v1 = v1 * r * w[j + 1];
+        }
+        if (rotate && c < rot_dims) {
+          const float sn = sin_t[c >> 1], cs = cos_t[c >> 1];
+          const float u = v0, v = v1;
+          v0 = u * cs - v * sn;
+          v1 = v * cs + u * sn;
+        }
+      }
+      if (is_q) {
+        dst = qd + i;
+      } else {
+        if (slot == 0) continue;
+        const int kvh = j / d;
+        dst = k_cache + ((static_cast<size_t>(page) * nkv + kvh) * page_size + offset) * d + c;
+      }
+    } else {
+      if (slot == 0) continue;
+      const int j = i - nq - nk, kvh = j / dv, c = j - kvh * dv;
+      dst = v_cache + ((static_cast<size_t>(page) * nkv + kvh) * page_size + offset) * dv + c;
+    }
+    if constexpr (sizeof(T) == 4) {
+      *reinterpret_cast<float2*>(dst) = make_float2(v0, v1);
+    } else {
+      *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(v0, v1);
+    }
   }
 }
 
-B200_EXPORT int b200_heads_prepare(const void* x, int dtype, int in_stride, const float* bias, const float* q_w,
-                                   const float* k_w, float eps, const float* inv_freq, int rot_dims, int interleaved,
-                                   const int* positions, const int* slots, int tokens, int nh, int nkv, int d, int dv,
-                                   int page_size, long long cache_slots, void* q_out, void* k_cache, void* v_cache,
-                                   int* err, cudaStream_t stream) {
-  if (tokens <= 0) return 0;
-  if (nh <= 0 || nkv <= 0 || d <= 0 || dv <= 0 || d > MAX_VEC || dv > MAX_VEC || rot_dims < 0 || rot_dims > d ||
-      (rot_dims & 1) || page_size <= 0)
-    return B200_BAD_SIZE;
-  const long long work = static_cast<long long>(tokens) * (nh + 2 * nkv);
-  const unsigned blocks = static_cast<unsigned>((work + WARPS - 1) / WARPS);
-  if (dtype == B200_F32)
-    heads_prepare_kernel<float><<<blocks, WARPS * 32, 0, stream>>>(
-        static_cast<const float*>(x), in_stride, bias, q_w, k_w, eps, inv_freq, rot_dims, interleaved, positions, slots,
-        tokens, nh, nkv, d, dv, page_size, cache_slots, static_cast<float*>(q_out), static_cast<float*>(k_cache),
-        static_cast<float*>(v_cache), err);
-  else if (dtype == B200_BF16)
-    heads_prepare_kernel<__nv_bfloat16><<<blocks, WARPS * 32, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(x), in_stride, bias, q_w, k_w, eps, inv_freq, rot_dims, interleaved,
-        positions, slots, tokens, nh, nkv, d, dv, page_size, cache_slots, static_cast<__nv_bfloat16*>(q_out),
-        static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), err);
-  else
-    return B200_BAD_DTYPE;
-  return b200_check_launch();
-}
-
-B200_EXPORT int b200_latent_prepare(const void* x, int dtype, int in_stride, const void* q_lat, const float* w_c,
-                                    float eps, const float* inv_freq, int rot_dims, int interleaved,
-                                    const int* positions, const int* slots, int tokens, int nh, int d, int r, int c_dim,
-                                    int page_size, long long cache_slots, void* q_out, void* k_cache, void* v_cache,
-                                    int* err, cudaStream_t stream) {
-  if (tokens <= 0) return 0;
-  if (nh <= 0 || d <= 0 || r < 0 || c_dim <= 0 || c_dim + r > MAX_VEC || rot_dims < 0 || rot_dims > r ||
-      (rot_dims & 1) || page_size <= 0)
-    return B200_BAD_SIZE;
-  const long long work = static_cast<long long>(tokens) * (nh + 1);
-  const unsigned blocks = static_cast<unsigned>((work + WARPS - 1) / WARPS);
-  if (dtype == B200_F32)
-    latent_prepare_kernel<float><<<blocks, WARPS * 32, 0, stream>>>(
-        static_cast<const float*>(x), in_stride, static_cast<const float*>(q_lat), w_c, eps, inv_freq, rot_dims,
-        interleaved, positions, slots, tokens, nh, d, r, c_dim, page_size, cache_slots, static_cast<float*>(q_out),
-        static_cast<float*>(k_cache), static_cast<float*>(v_cache), err);
-  else if (dtype == B200_BF16)
-    latent_prepare_kernel<__nv_bfloat16><<<blocks, WARPS * 32, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(x), in_stride, static_cast<const __nv_bfloat16*>(q_lat), w_c, eps, inv_freq,
-        rot_dims, interleaved, positions, slots, tokens, nh, d, r, c_dim, page_size, cache_slots,
-        static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache),
-        err);
-  else
-    return B200_BAD_DTYPE;
-  return b200_check_launch();
-}
 
 // (3): norms over the whole q and the whole k projection.  has_kv 0: x holds q columns only, nothing is stored.
 B200_EXPORT int b200_joint_heads_prepare(const void* x, int dtype, int in_stride, const float* bias, const float* q_w,
@@ -290,9 +296,12 @@ B200_EXPORT int b200_joint_heads_prepare(const void* x, int dtype, int in_stride
                                          int nkv, int d, int dv, int has_kv, int page_size, long long cache_slots,
                                          void* q_out, void* k_cache, void* v_cache, int* err, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (nh <= 0 || nkv <= 0 || d <= 0 || dv <= 0 || rot_dims < 0 || rot_dims > d || (rot_dims & 1) || page_size <= 0)
+  if (nh <= 0 || nkv <= 0 || d <= 0 || dv <= 0 || rot_dims < 0 || rot_dims > d || (rot_dims & 1) || page_size <= 0 ||
+      (d & 1) || (dv & 1))                            // columns are taken two at a time
     return B200_BAD_SIZE;
-  const size_t smem = (static_cast<size_t>(nh) * d + (has_kv ? static_cast<size_t>(nkv) * (d + dv) : 0)) * sizeof(float);
+  const size_t smem = (static_cast<size_t>(nh) * d + (has_kv ? static_cast<size_t>(nkv) * (d + dv) : 0) + rot_dims) *
+                      sizeof(float);
+  const int threads = tokens <= 64 ? 1024 : 256;     // few tokens: more threads each, the step waits for the slowest
   if (smem > 200 * 1024) return B200_BAD_SIZE;
 #define B200_JOINT(T)                                                                                               \
   do {                                                                                                              \
@@ -301,7 +310,7 @@ B200_EXPORT int b200_joint_heads_prepare(const void* x, int dtype, int in_stride
                                            static_cast<int>(smem));                                                 \
       if (e != cudaSuccess) return static_cast<int>(e);                                                             \
     }                                                                                                               \
-    joint_heads_prepare_kernel<T><<<tokens, 256, smem, stream>>>(                                                   \
+    joint_heads_prepare_kernel<T><<<tokens, threads, smem, stream>>>(                                                   \
         static_cast<const T*>(x), in_stride, bias, q_w, k_w, eps, inv_freq, rot_dims, interleaved, positions, slots, \
         nh, nkv, d, dv, has_kv, page_size, cache_slots, static_cast<T*>(q_out), static_cast<T*>(k_cache),           \
         static_cast<T*>(v_cache), err);                                                                             \

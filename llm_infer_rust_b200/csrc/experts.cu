@@ -301,37 +301,72 @@ expert_combine_kernel(float* __restrict__ out, const float* __restrict__ Y, cons
 // sigmoid of each), experts in `groups` equal groups of neighbours, a group's score its largest score, only experts
 // of the `keep` best groups can be chosen, the `top` largest of them are, each weighted by its score (divided by
 // the chosen scores' sum if `renormalize`).  Ties go to the lower index.
-// A block takes ROUTER_TOKENS tokens: warp w multiplies experts w, w + 8, .. for all of them (a row of W is read
-// once a block; a logit's additions do not depend on which other tokens share the block), then warp t chooses for
-// token t.  Shared memory: ROUTER_TOKENS * experts floats (logits, then scores) and as many ints.
-constexpr int ROUTER_TOKENS = 8, ROUTER_WARPS = 8;
+// A block takes TT tokens (1 for a step of few tokens, so that they spread over the SMs; 4 otherwise): warp w
+// multiplies experts 2w, 2w + 1, then 2w + 16, .. for all of them (a row of W is read once a block), then warp t
+// chooses for token t.  A logit is summed the same way whatever the block holds: lane l takes columns
+// 8 l .. 8 l + 7, then 256 further on and so on, in order, and the lanes' sums meet in a butterfly.  Rows that start
+// on 16 bytes are read in 16-byte pieces.  Shared memory: TT * experts floats (logits, then scores) and as many ints.
+constexpr int ROUTER_WARPS = 8;
 
-template <typename TX, typename TW>
+template <typename TX, typename TW, int TT>
 __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 expert_router_kernel(const TX* __restrict__ x, const TW* __restrict__ W, int tokens, int width, int experts,
                      int groups, int keep, int top, int sigmoid_scores, int renormalize, int* __restrict__ choice,
                      float* __restrict__ weight) {
   extern __shared__ float rsm[];
-  float* z = rsm;                                                   // [ROUTER_TOKENS][experts]
-  int* open = reinterpret_cast<int*>(rsm + ROUTER_TOKENS * experts);   // [ROUTER_TOKENS][experts]: may still be chosen
+  float* z = rsm;                                                   // [TT][experts]
+  int* open = reinterpret_cast<int*>(rsm + TT * experts);           // [TT][experts]: may still be chosen
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int t0 = blockIdx.x * ROUTER_TOKENS;
-  const int nt = min(ROUTER_TOKENS, tokens - t0);
-  for (int e = warp; e < experts; e += ROUTER_WARPS) {
-    float acc[ROUTER_TOKENS];
+  const int t0 = blockIdx.x * TT;
+  const int nt = min(TT, tokens - t0);
+  const bool wide = width % 8 == 0;                                 // every row of x and W starts on 16 bytes
+  for (int e0 = 2 * warp; e0 < experts; e0 += 2 * ROUTER_WARPS) {
+    const bool two = e0 + 1 < experts;
+    float acc[2][TT];
 #pragma unroll
-    for (int i = 0; i < ROUTER_TOKENS; ++i) acc[i] = 0.0f;
-    const TW* w = W + static_cast<size_t>(e) * width;
-    for (int k = lane; k < width; k += 32) {
-      const float wk = to_f32<TW>(w[k]);
+    for (int i = 0; i < TT; ++i) acc[0][i] = acc[1][i] = 0.0f;
+    const TW* w0 = W + static_cast<size_t>(e0) * width;
+    const TW* w1 = W + static_cast<size_t>(two ? e0 + 1 : e0) * width;
+    const TX* xs = x + static_cast<size_t>(t0) * width;
+    if (wide) {
+#pragma unroll 2
+      for (int k = lane * 8; k < width; k += 256) {
+        float a[8], b[8];
+        load_floats<TW, 8>(w0 + k, a);
+        load_floats<TW, 8>(w1 + k, b);
 #pragma unroll
-      for (int i = 0; i < ROUTER_TOKENS; ++i)
-        if (i < nt) acc[i] = fmaf(wk, to_f32<TX>(x[static_cast<size_t>(t0 + i) * width + k]), acc[i]);
+        for (int i = 0; i < TT; ++i) {               // a token beyond the last reads the last one's row; its sums are dropped
+          float v[8];
+          load_floats<TX, 8>(xs + static_cast<size_t>(min(i, nt - 1)) * width + k, v);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            acc[0][i] = fmaf(a[j], v[j], acc[0][i]);
+            acc[1][i] = fmaf(b[j], v[j], acc[1][i]);
+          }
+        }
+      }
+    } else {
+      for (int k8 = lane * 8; k8 < width; k8 += 256) {
+        const int end = min(k8 + 8, width);
+        for (int k = k8; k < end; ++k) {
+          const float a = to_f32<TW>(w0[k]), b = to_f32<TW>(w1[k]);
+#pragma unroll
+          for (int i = 0; i < TT; ++i)
+            if (i < nt) {
+              const float v = to_f32<TX>(xs[static_cast<size_t>(i) * width + k]);
+              acc[0][i] = fmaf(a, v, acc[0][i]);
+              acc[1][i] = fmaf(b, v, acc[1][i]);
+            }
+        }
+      }
     }
 #pragma unroll
-    for (int i = 0; i < ROUTER_TOKENS; ++i) {
-      const float v = warp_sum(acc[i]);
-      if (lane == 0) z[i * experts + e] = v;
+    for (int i = 0; i < TT; ++i) {
+      const float v0 = warp_sum(acc[0][i]), v1 = warp_sum(acc[1][i]);
+      if (lane == 0 && i < nt) {
+        z[i * experts + e0] = v0;
+        if (two) z[i * experts + e0 + 1] = v1;
+      }
     }
   }
   __syncthreads();
@@ -510,18 +545,25 @@ B200_EXPORT int b200_expert_router(const void* x, int x_dtype, const void* w, in
   if (width <= 0 || experts <= 0 || groups <= 0 || experts % groups || keep <= 0 || keep > groups || top <= 0 ||
       top > keep * (experts / groups))
     return B200_BAD_SIZE;
-  const size_t smem = static_cast<size_t>(ROUTER_TOKENS) * experts * (sizeof(float) + sizeof(int));
-  if (smem > 48 * 1024) return B200_BAD_SIZE;
-  const unsigned blocks = (tokens + ROUTER_TOKENS - 1) / ROUTER_TOKENS;
-#define B200_ROUTER(TX, TW)                                                                                          \
-  expert_router_kernel<TX, TW><<<blocks, ROUTER_WARPS * 32, smem, stream>>>(                                         \
+  const int per_block = tokens <= 148 ? 1 : 4;
+  const size_t smem = static_cast<size_t>(per_block) * experts * (sizeof(float) + sizeof(int));
+  if (static_cast<size_t>(8) * experts * (sizeof(float) + sizeof(int)) > 48 * 1024) return B200_BAD_SIZE;
+  const unsigned blocks = (tokens + per_block - 1) / per_block;
+#define B200_ROUTER_TT(TX, TW, TT)                                                                                   \
+  expert_router_kernel<TX, TW, TT><<<blocks, ROUTER_WARPS * 32, smem, stream>>>(                                     \
       static_cast<const TX*>(x), static_cast<const TW*>(w), tokens, width, experts, groups, keep, top, sigmoid_scores, \
       renormalize, choice, weight)
+#define B200_ROUTER(TX, TW)                                                                                          \
+  do {                                                                                                               \
+    if (per_block == 1) B200_ROUTER_TT(TX, TW, 1);                                                                   \
+    else B200_ROUTER_TT(TX, TW, 4);                                                                                  \
+  } while (0)
   if (x_dtype == B200_F32 && w_dtype == B200_F32) B200_ROUTER(float, float);
   else if (x_dtype == B200_BF16 && w_dtype == B200_BF16) B200_ROUTER(__nv_bfloat16, __nv_bfloat16);
   else if (x_dtype == B200_BF16 && w_dtype == B200_F32) B200_ROUTER(__nv_bfloat16, float);
   else if (x_dtype == B200_F32 && w_dtype == B200_BF16) B200_ROUTER(float, __nv_bfloat16);
   else return B200_BAD_DTYPE;
+#undef B200_ROUTER_TT
 #undef B200_ROUTER
   return b200_check_launch();
 }

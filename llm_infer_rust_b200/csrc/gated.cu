@@ -386,6 +386,139 @@ B200_EXPORT int b200_act_table_mul(void* out, const void* z, const void* table, 
   return b200_check_launch();
 }
 
+// The whole gated read of a second token table for a step of few tokens, one block a token, where four launches
+// would each move a few kilobytes:
+//   z = Wg x (rounded to T);  g = act(z) * table[id][column ..] (rounded to T);  y = Wp g (float)
+//   stream <- stream + y / sqrt(mean(y^2) + eps) * norm;   cast_out <- the new stream rounded to T (if given)
+// x [tokens, width] is the stream rounded to T (the stream itself in float32; it is read before it is written).
+// Wg [dim, width], Wp [width, dim].  A warp takes four rows of Wg at a time, its lanes eight columns each and then 256
+// further on, in order; a thread takes a row of Wp.  Shared memory: dim + width floats.
+constexpr int SIDE_THREADS = 512;
+
+template <typename T>
+__global__ void __launch_bounds__(SIDE_THREADS)
+token_side_few_kernel(float* stream, const T* x, const T* __restrict__ gate, const T* __restrict__ table,
+                      const int* __restrict__ ids, const T* __restrict__ proj, const float* __restrict__ norm_w,
+                      float eps, T* __restrict__ cast_out, int vocab, int table_width, int column, int dim, int width,
+                      int act, int* err) {
+  __shared__ float part[SIDE_THREADS / 32];
+  extern __shared__ float side_sm[];
+  float* g = side_sm;                                // dim
+  float* y = side_sm + dim;                          // width
+  const size_t t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) atomicOr(err, B200_ERR_TOKEN_RANGE);
+    id = 0;
+  }
+  const T* e = table + static_cast<size_t>(id) * table_width + column;
+  const T* xr = x + t * width;
+  const bool wide = width % 8 == 0;
+  constexpr int NW = SIDE_THREADS / 32;
+  for (int jb = 0; jb < dim; jb += 4 * NW) {         // four rows of Wg a warp at a time: one read of x serves them all
+    const T* w[4];
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int r = 0; r < 4; ++r) w[r] = gate + static_cast<size_t>(min(jb + warp + r * NW, dim - 1)) * width;
+    if (wide) {
+#pragma unroll 2
+      for (int k = lane * 8; k < width; k += 256) {
+        float b[8];
+        load_floats<T, 8>(xr + k, b);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          float a[8];
+          load_floats<T, 8>(w[r] + k, a);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[r] = fmaf(a[i], b[i], acc[r]);
+        }
+      }
+    } else {
+      for (int k8 = lane * 8; k8 < width; k8 += 256) {
+        const int end = min(k8 + 8, width);
+        for (int k = k8; k < end; ++k) {
+          const float b = to_f32<T>(xr[k]);
+#pragma unroll
+          for (int r = 0; r < 4; ++r) acc[r] = fmaf(to_f32<T>(w[r][k]), b, acc[r]);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const float sum = warp_sum(acc[r]);
+      const int j = jb + warp + r * NW;
+      if (lane == 0 && j < dim) {
+        const float z = to_f32<T>(from_f32<T>(sum));
+        g[j] = to_f32<T>(from_f32<T>(activate(z, act) * to_f32<T>(e[j])));
+      }
+    }
+  }
+  __syncthreads();
+  float ss = 0.0f;
+  const bool wide_dim = dim % 8 == 0;
+  for (int c = threadIdx.x; c < width; c += SIDE_THREADS) {
+    const T* w = proj + static_cast<size_t>(c) * dim;
+    float acc = 0.0f;
+    if (wide_dim) {
+#pragma unroll 4
+      for (int k = 0; k < dim; k += 8) {
+        float a[8];
+        load_floats<T, 8>(w + k, a);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc = fmaf(a[i], g[k + i], acc);
+      }
+    } else {
+      for (int k = 0; k < dim; ++k) acc = fmaf(to_f32<T>(w[k]), g[k], acc);
+    }
+    y[c] = acc;
+    ss = fmaf(acc, acc, ss);
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) part[warp] = ss;
+  __syncthreads();
+  ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < SIDE_THREADS / 32; ++i) ss += part[i];
+  const float r = 1.0f / sqrtf(ss / static_cast<float>(width) + eps);
+  float* sr = stream + t * width;
+  for (int c = threadIdx.x; c < width; c += SIDE_THREADS) {
+    const float s = sr[c] + y[c] * r * norm_w[c];
+    sr[c] = s;
+    if (cast_out != nullptr) cast_out[t * width + c] = from_f32<T>(s);
+  }
+}
+
+// dtype: of x, gate, table, proj and cast_out (null: none is written; in float32 x may be the stream itself).
+B200_EXPORT int b200_token_side_few(float* stream, const void* x, const void* gate, const void* table, const int* ids,
+                                    const void* proj, const float* norm_w, float eps, void* cast_out, int tokens,
+                                    int vocab, int table_width, int column, int dim, int width, int act, int dtype,
+                                    int* err, cudaStream_t stream_) {
+  if (tokens <= 0) return 0;
+  if (act < ACT_SILU || act > ACT_RELU_SQUARED || vocab <= 0 || dim <= 0 || width <= 0 || column < 0 ||
+      column + dim > table_width)
+    return B200_BAD_SIZE;
+  const size_t smem = (static_cast<size_t>(dim) + width) * sizeof(float);
+  if (smem > 200 * 1024) return B200_BAD_SIZE;
+#define B200_SIDE(T)                                                                                               \
+  do {                                                                                                             \
+    if (smem > 48 * 1024) {                                                                                        \
+      cudaError_t e = cudaFuncSetAttribute(token_side_few_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                                           static_cast<int>(smem));                                                \
+      if (e != cudaSuccess) return static_cast<int>(e);                                                            \
+    }                                                                                                              \
+    token_side_few_kernel<T><<<tokens, SIDE_THREADS, smem, stream_>>>(                                             \
+        stream, static_cast<const T*>(x), static_cast<const T*>(gate), static_cast<const T*>(table), ids,          \
+        static_cast<const T*>(proj), norm_w, eps, static_cast<T*>(cast_out), vocab, table_width, column, dim,      \
+        width, act, err);                                                                                          \
+  } while (0)
+  if (dtype == B200_F32) B200_SIDE(float);
+  else if (dtype == B200_BF16) B200_SIDE(__nv_bfloat16);
+  else return B200_BAD_DTYPE;
+#undef B200_SIDE
+  return b200_check_launch();
+}
+
 // y[t][c] += bias[c], the sum taken in float and rounded once (a projection's bias where nothing else can take it).
 template <typename T>
 __global__ void __launch_bounds__(256) add_row_bias_kernel(T* __restrict__ y, const float* __restrict__ bias, int width) {

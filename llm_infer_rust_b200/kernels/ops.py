@@ -1917,6 +1917,40 @@ def act_table_mul(z: torch.Tensor, act: str, table: torch.Tensor, ids: torch.Ten
     return out
 
 
+TOKEN_SIDE_FEW = 16     # a step of at most this many tokens takes the one-kernel form of the token table's gated read
+
+
+def token_side_few(stream: torch.Tensor, x: torch.Tensor, gate: torch.Tensor, table: torch.Tensor, ids: torch.Tensor,
+                   column: int, proj: torch.Tensor, norm: torch.Tensor, eps: float, act: str,
+                   cast_to: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """For a step of few tokens, in one kernel: g = act(gate x) * table[ids, column : column + dim]; y = proj g;
+    stream <- stream + y / sqrt(mean(y^2) + eps) * norm, in place on the float32 ``stream``.  ``x`` is the stream
+    rounded to the dtype of gate, table and proj (the stream itself in float32).  Returns as ``norm_add`` does."""
+    _cuda(stream, x, gate, table, ids, proj, norm)
+    _contig(stream, x, gate, table, ids, proj, norm)
+    _f32(stream, norm)
+    _i32(ids)
+    tokens, width = stream.shape
+    dim = gate.shape[0]
+    if act not in ACTIVATIONS or tuple(x.shape) != (tokens, width) or tuple(gate.shape) != (dim, width) or \
+            tuple(proj.shape) != (width, dim) or norm.numel() != width or ids.numel() != tokens or \
+            not (x.dtype == gate.dtype == table.dtype == proj.dtype) or column + dim > table.shape[1]:
+        raise KernelError("token_side_few: sizes or dtypes do not fit")
+    out = None
+    if cast_to is not None and cast_to != torch.float32:
+        if cast_to != x.dtype:
+            raise KernelError("token_side_few: the rounded copy has the dtype of x")
+        out = torch.empty((tokens, width), dtype=cast_to, device=x.device)
+    rc = _gated().b200_token_side_few(
+        _p(stream), _p(x), _p(gate), _p(table), _p(ids), _p(proj), _p(norm), ctypes.c_float(eps), _p(out), tokens,
+        table.shape[0], table.shape[1], int(column), dim, width, ACTIVATIONS[act], _code(x), _p(error_word(x.device)),
+        _stream())
+    _ok(rc, "token_side_few")
+    if cast_to is None:
+        return None
+    return out if out is not None else stream
+
+
 # --------------------------------------------------------------------------- a float stream with norms on the outputs
 def norm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, bias: Optional[torch.Tensor] = None,
              cast_to: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:

@@ -17,7 +17,8 @@ class TokenSideInput(Part):
     ``table`` [vocab, table_width] is one table for all layers (every layer's part is bound to the same tensor and
     reads its own ``dim`` columns from ``column`` on); ``gate_proj`` [dim, hidden], ``out_proj`` [hidden, dim],
     ``norm`` [hidden] a plain RMS-norm weight; ``activation`` by name (``ops.ACTIVATIONS``).  The products read the
-    stream rounded to the engine's dtype; the activation, the norm and the add are taken in float."""
+    stream rounded to the engine's dtype; the activation, the norm and the add are taken in float.  A step of few
+    tokens (``ops.TOKEN_SIDE_FEW``) takes one kernel for all of it; its y stays in float instead of being rounded."""
     category = "token_side"
 
     def __init__(self, spec, env):
@@ -47,6 +48,9 @@ class TokenSideInput(Part):
         """``stream``: the float32 x (changed in place); ``x``: the same rounded to the engine's dtype.  Returns the
         new stream rounded to the engine's dtype."""
         p = self.params
+        if x.shape[0] <= ops.TOKEN_SIDE_FEW:       # a decode step: one kernel instead of four
+            return ops.token_side_few(stream, x, p["gate_proj"], p["table"], ctx.token_ids, self.column, p["out_proj"],
+                                      p["norm"], self.eps, self.activation, cast_to=self.env.dtype)
         z = ops.linear(x, p["gate_proj"])
         g = ops.act_table_mul(z, self.activation, p["table"], ctx.token_ids, self.column)
         y = ops.linear(g, p["out_proj"])

@@ -135,21 +135,21 @@ def route(z: torch.Tensor, top: int, groups: int, keep: int):
     return chosen, s.gather(1, chosen)
 
 
-def route_margin(z: torch.Tensor, top: int, groups: int, keep: int) -> float:
-    """How far the router's choice is from another one, in logits, at its closest token: the gap between the last
-    group kept and the first one left out (by their largest logits), and between the last expert chosen and the first
-    one left out among the experts of the kept groups.  A choice within rounding of another is a close call."""
+def route_margin(z: torch.Tensor, top: int, groups: int, keep: int) -> torch.Tensor:
+    """How far every token's choice is from another one, in logits [T]: the gap between the last group kept and the
+    first one left out (by their largest logits), and between the last expert chosen and the first one left out among
+    the experts of the kept groups.  A choice within rounding of another is a close call."""
     T, E = z.shape
     per = E // groups
     best = z.reshape(T, groups, per).max(-1).values.sort(-1, descending=True).values
-    gap = float("inf")
+    gap = torch.full((T,), float("inf"), dtype=z.dtype)
     if keep < groups:
-        gap = min(gap, float((best[:, keep - 1] - best[:, keep]).min()))
+        gap = torch.minimum(gap, best[:, keep - 1] - best[:, keep])
     chosen_groups = z.reshape(T, groups, per).max(-1).values.topk(keep, -1).indices
     allowed = torch.zeros(T, groups, dtype=torch.bool).scatter_(1, chosen_groups, True).repeat_interleave(per, 1)
     ranked = z.masked_fill(~allowed, float("-inf")).sort(-1, descending=True).values
     if top < keep * per:
-        gap = min(gap, float((ranked[:, top - 1] - ranked[:, top]).min()))
+        gap = torch.minimum(gap, ranked[:, top - 1] - ranked[:, top])
     return gap
 
 
@@ -181,7 +181,7 @@ def token_side(x: torch.Tensor, ids: List[int], w: Dict[str, torch.Tensor], p: s
 def forward(config: dict, weights: Dict[str, torch.Tensor], ids: List[int], dtype=torch.float64,
             layers_out: Optional[list] = None, margins_out: Optional[list] = None) -> torch.Tensor:
     """Logits [T, vocab] of one whole sequence.  ``layers_out``: a list that receives x after every layer;
-    ``margins_out``: one that receives every router's ``route_margin``."""
+    ``margins_out``: one that receives every router's ``route_margin`` [T]."""
     w = {n: (t if not t.is_floating_point() else t.to(dtype)) for n, t in weights.items()}
     eps = config["norm"]["eps"]
     side = config.get("token_side")

@@ -242,6 +242,34 @@ def test_activations_gates_bias_and_the_token_table(dtype, width):
     ops.check_errors(dev)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tokens,width,dim,layer", [(1, 40, 6, 2), (7, 264, 16, 0), (16, 72, 1, 3), (3, 1032, 24, 1)])
+def test_token_table_read_of_a_few_tokens_in_one_kernel(tokens, width, dim, layer, dtype):
+    """The gated read of the layer's columns of the second table, normed and added into the float stream, for a step
+    of few tokens (one kernel) against the plain function; the rounded copy is the new stream rounded once."""
+    from llm_infer_rust_b200.kernels import ops
+    dev = torch.device("cuda")
+    g = torch.Generator().manual_seed(width + dim)
+    vocab, layers, eps = 37, 4, 1e-5
+    w = {"side.embed": K.bf16_values(torch.randn(vocab, layers * dim, generator=g)),
+         "s.side.gate": K.bf16_values(torch.randn(dim, width, generator=g) * width ** -0.5),
+         "s.side.proj": K.bf16_values(torch.randn(width, dim, generator=g)),
+         "s.side.norm": 0.7 + 0.3 * torch.randn(width, generator=g)}
+    ids = torch.randint(0, vocab, (tokens,), generator=g).tolist()
+    stream = torch.randn(tokens, width, generator=g) * 2
+    x = K.bf16_values(stream) if dtype == torch.bfloat16 else stream
+    want = stream.double() + P.token_side(x.double(), ids, {n: t.double() for n, t in w.items()}, "s.", layer, dim, eps)
+    s_dev = stream.to(dev).clone()
+    x_dev = s_dev if dtype == torch.float32 else x.to(dev, dtype)
+    got = ops.token_side_few(s_dev, x_dev, w["s.side.gate"].to(dev, dtype), w["side.embed"].to(dev, dtype), _i32(ids),
+                             layer * dim, w["s.side.proj"].to(dev, dtype), w["s.side.norm"].to(dev), eps, "gelu_tanh",
+                             cast_to=dtype)
+    tol = 3e-5 if dtype == torch.float32 else 3e-2
+    torch.testing.assert_close(s_dev.cpu().double(), want, rtol=tol, atol=tol)
+    assert torch.equal(got, s_dev.to(dtype))
+    ops.check_errors(dev)
+
+
 def _attend_in_portions(q, k, v, portions, dtype, chunk, scale, page=8):
     """q [T, H, d], k [T, G, d], v [T, G, dv] stored in pages handed out in a scrambled order and read by the attention
     kernels portion by portion, with the sink of score 0; the outputs [T, H, dv]."""
@@ -319,14 +347,14 @@ def test_whole_decoded_and_in_portions(name, dtype, models):
     raw, w, folder = models[name]
     T = 150
     ids = K.tokens(raw["vocab"], T, 3)
-    want = K.oracle(raw, w, ids)
+    want, close = K.oracle_and_close_calls(raw, w, ids)
     eng = K.make_engine(folder, dtype, page_size=8, pool_tokens=256)
     tol = K.tolerance(name, dtype)
-    K.check(K.run_alone(eng, 1, ids, [T]), want, dtype, "whole", tol)
-    K.check(K.run_alone(eng, 2, ids, [T - 40] + [1] * 40), want, dtype, "last 40 decoded", tol)
-    K.check(K.run_alone(eng, 3, ids, cut(T, PORTIONS)), want, dtype, "in portions", tol)
-    K.check(K.run_alone(eng, 4, ids[:24], [1] * 24), want[:24], dtype, "token by token from the first", tol)
-    K.check(K.run_alone(eng, 5, ids[:61], [2] * 30 + [1]), want[:61], dtype, "two tokens at a time", tol)
+    K.check_clear(K.run_alone(eng, 1, ids, [T]), want, close, dtype, "whole", tol)
+    K.check_clear(K.run_alone(eng, 2, ids, [T - 40] + [1] * 40), want, close, dtype, "last 40 decoded", tol)
+    K.check_clear(K.run_alone(eng, 3, ids, cut(T, PORTIONS)), want, close, dtype, "in portions", tol)
+    K.check_clear(K.run_alone(eng, 4, ids[:24], [1] * 24), want[:24], close[:24], dtype, "token by token from the first", tol)
+    K.check_clear(K.run_alone(eng, 5, ids[:61], [2] * 30 + [1]), want[:61], close[:61], dtype, "two tokens at a time", tol)
     assert eng.cache.manager.check() == ""
 
 
@@ -407,12 +435,12 @@ def test_configurations_drawn_at_random(seed, tmp_path):
     ids = K.tokens(raw["vocab"], T, seed)
     w = K.clear_weights(raw, 700 + seed, ids)
     folder = K.write_model(str(tmp_path / "m"), raw, w)
-    want = K.oracle(raw, w, ids)
+    want, close = K.oracle_and_close_calls(raw, w, ids)
     for dtype in ("float32", "bfloat16"):
         eng = K.make_engine(folder, dtype, page_size=(4, 8, 16)[seed % 3], pool_tokens=256)
-        K.check(K.run_alone(eng, 1, ids, [T]), want, dtype, f"{seed} whole")
-        K.check(K.run_alone(eng, 2, ids, [T - 30] + [1] * 30), want, dtype, f"{seed} last 30 decoded")
-        K.check(K.run_alone(eng, 3, ids, cut(T, [2, 17, 3, 40, 1, 5])), want, dtype, f"{seed} in portions")
+        K.check_clear(K.run_alone(eng, 1, ids, [T]), want, close, dtype, f"{seed} whole")
+        K.check_clear(K.run_alone(eng, 2, ids, [T - 30] + [1] * 30), want, close, dtype, f"{seed} last 30 decoded")
+        K.check_clear(K.run_alone(eng, 3, ids, cut(T, [2, 17, 3, 40, 1, 5])), want, close, dtype, f"{seed} in portions")
         assert eng.cache.manager.check() == ""
         del eng
 
@@ -444,7 +472,7 @@ def test_mixed_batches_with_pages_and_slots_used_again(name, dtype, models):
     raw, w, folder = models[name]
     lengths = {"a": 90, "b": 37, "c": 120, "d": 5, "e": 64, "f": 101}
     reqs = {r: (K.tokens(raw["vocab"], n, 20 + i), max(2, n - 12 - i)) for i, (r, n) in enumerate(lengths.items())}
-    want = {r: K.oracle(raw, w, ids) for r, (ids, _) in reqs.items()}
+    want = {r: K.oracle_and_close_calls(raw, w, ids) for r, (ids, _) in reqs.items()}
     eng = K.make_engine(folder, dtype, page_size=8, pool_tokens=320, max_requests=3)
     got = {r: [] for r in reqs}
     number = {r: i + 1 for i, r in enumerate(reqs)}
@@ -466,7 +494,7 @@ def test_mixed_batches_with_pages_and_slots_used_again(name, dtype, models):
         assert eng.cache.manager.check() == ""
     eng.check_kernel_errors()
     for r in reqs:
-        K.check(np.concatenate(got[r]), want[r], dtype, f"request {r} in mixed batches")
+        K.check_clear(np.concatenate(got[r]), *want[r], dtype, f"request {r} in mixed batches")
 
 
 def test_pages_that_are_used_again_hold_nothing_of_their_last_user(models):
@@ -483,7 +511,8 @@ def test_long_decoding(dtype, models):
     raw, w, folder = models["T1"]
     ids = K.tokens(raw["vocab"], 260, 8)
     eng = K.make_engine(folder, dtype, page_size=16, pool_tokens=320)
-    K.check(K.run_alone(eng, 1, ids, [6] + [1] * 254), K.oracle(raw, w, ids), dtype, "254 tokens decoded one by one")
+    K.check_clear(K.run_alone(eng, 1, ids, [6] + [1] * 254), *K.oracle_and_close_calls(raw, w, ids), dtype,
+                  "254 tokens decoded one by one")
 
 
 @pytest.mark.parametrize("dtype,graphs,portion_graphs", [("float32", 0, 0), ("bfloat16", 0, 0), ("bfloat16", 4, 0),
@@ -513,11 +542,11 @@ def test_trace_replay_as_a_user_runs_it(models, tmp_path):
     from replay_driver import Replay, run_alone
     raw, w, folder = models["T3"]
     ids = K.tokens(raw["vocab"], 70, 9)
-    want = K.oracle(raw, w, ids)
+    want, close = K.oracle_and_close_calls(raw, w, ids)
     for dtype in ("bfloat16", "float32"):
         rp = Replay(folder, dtype, 128, str(tmp_path / dtype), raw["vocab"], ["--page-size", "8"])
         try:
-            K.check(run_alone(rp, "x", ids, [33, 2, 3] + [1] * 32), want, dtype, "replay")
+            K.check_clear(run_alone(rp, "x", ids, [33, 2, 3] + [1] * 32), want, close, dtype, "replay")
         finally:
             assert rp.close() == 0
 

