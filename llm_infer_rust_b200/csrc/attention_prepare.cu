@@ -289,6 +289,59 @@ joint_heads_prepare_kernel(const T* __restrict__ x, int in_stride, const float* 
 }
 
 
+B200_EXPORT int b200_heads_prepare(const void* x, int dtype, int in_stride, const float* bias, const float* q_w,
+                                   const float* k_w, float eps, const float* inv_freq, int rot_dims, int interleaved,
+                                   const int* positions, const int* slots, int tokens, int nh, int nkv, int d, int dv,
+                                   int page_size, long long cache_slots, void* q_out, void* k_cache, void* v_cache,
+                                   int* err, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (nh <= 0 || nkv <= 0 || d <= 0 || dv <= 0 || d > MAX_VEC || dv > MAX_VEC || rot_dims < 0 || rot_dims > d ||
+      (rot_dims & 1) || page_size <= 0)
+    return B200_BAD_SIZE;
+  const long long work = static_cast<long long>(tokens) * (nh + 2 * nkv);
+  const unsigned blocks = static_cast<unsigned>((work + WARPS - 1) / WARPS);
+  if (dtype == B200_F32)
+    heads_prepare_kernel<float><<<blocks, WARPS * 32, 0, stream>>>(
+        static_cast<const float*>(x), in_stride, bias, q_w, k_w, eps, inv_freq, rot_dims, interleaved, positions, slots,
+        tokens, nh, nkv, d, dv, page_size, cache_slots, static_cast<float*>(q_out), static_cast<float*>(k_cache),
+        static_cast<float*>(v_cache), err);
+  else if (dtype == B200_BF16)
+    heads_prepare_kernel<__nv_bfloat16><<<blocks, WARPS * 32, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), in_stride, bias, q_w, k_w, eps, inv_freq, rot_dims, interleaved,
+        positions, slots, tokens, nh, nkv, d, dv, page_size, cache_slots, static_cast<__nv_bfloat16*>(q_out),
+        static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), err);
+  else
+    return B200_BAD_DTYPE;
+  return b200_check_launch();
+}
+
+B200_EXPORT int b200_latent_prepare(const void* x, int dtype, int in_stride, const void* q_lat, const float* w_c,
+                                    float eps, const float* inv_freq, int rot_dims, int interleaved,
+                                    const int* positions, const int* slots, int tokens, int nh, int d, int r, int c_dim,
+                                    int page_size, long long cache_slots, void* q_out, void* k_cache, void* v_cache,
+                                    int* err, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (nh <= 0 || d <= 0 || r < 0 || c_dim <= 0 || c_dim + r > MAX_VEC || rot_dims < 0 || rot_dims > r ||
+      (rot_dims & 1) || page_size <= 0)
+    return B200_BAD_SIZE;
+  const long long work = static_cast<long long>(tokens) * (nh + 1);
+  const unsigned blocks = static_cast<unsigned>((work + WARPS - 1) / WARPS);
+  if (dtype == B200_F32)
+    latent_prepare_kernel<float><<<blocks, WARPS * 32, 0, stream>>>(
+        static_cast<const float*>(x), in_stride, static_cast<const float*>(q_lat), w_c, eps, inv_freq, rot_dims,
+        interleaved, positions, slots, tokens, nh, d, r, c_dim, page_size, cache_slots, static_cast<float*>(q_out),
+        static_cast<float*>(k_cache), static_cast<float*>(v_cache), err);
+  else if (dtype == B200_BF16)
+    latent_prepare_kernel<__nv_bfloat16><<<blocks, WARPS * 32, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), in_stride, static_cast<const __nv_bfloat16*>(q_lat), w_c, eps, inv_freq,
+        rot_dims, interleaved, positions, slots, tokens, nh, d, r, c_dim, page_size, cache_slots,
+        static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache),
+        err);
+  else
+    return B200_BAD_DTYPE;
+  return b200_check_launch();
+}
+
 // (3): norms over the whole q and the whole k projection.  has_kv 0: x holds q columns only, nothing is stored.
 B200_EXPORT int b200_joint_heads_prepare(const void* x, int dtype, int in_stride, const float* bias, const float* q_w,
                                          const float* k_w, float eps, const float* inv_freq, int rot_dims,

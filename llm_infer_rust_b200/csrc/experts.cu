@@ -276,13 +276,37 @@ expert_gemm_bf16_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int*
 
 // ------------------------------------------------------------------ the experts' outputs back to the tokens
 // weight: one per pair, or null for `uniform` each.  add [tokens, width] (TA; a shared expert's output) joins the sum.
+// grid (tokens, column tiles of 1,024): a thread takes four neighbouring columns (one where the width is no multiple
+// of four); the sum over k runs in order either way.
 template <typename TA>
 __global__ void __launch_bounds__(256)
 expert_combine_kernel(float* __restrict__ out, const float* __restrict__ Y, const int* __restrict__ pos_of_pair,
                       int top, int width, float uniform, const float* __restrict__ weight,
                       const TA* __restrict__ add) {
   const size_t t = blockIdx.x;
-  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+  if (width % 4 == 0) {
+    const int c = (blockIdx.y * 256 + threadIdx.x) * 4;
+    if (c >= width) return;
+    float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int k = 0; k < top; ++k) {
+      const float4 v = *reinterpret_cast<const float4*>(Y + static_cast<size_t>(pos_of_pair[t * top + k]) * width + c);
+      if (weight == nullptr) {
+        s[0] += v.x; s[1] += v.y; s[2] += v.z; s[3] += v.w;
+      } else {
+        const float g = weight[t * top + k];
+        s[0] = fmaf(g, v.x, s[0]); s[1] = fmaf(g, v.y, s[1]); s[2] = fmaf(g, v.z, s[2]); s[3] = fmaf(g, v.w, s[3]);
+      }
+    }
+    if (weight == nullptr) { s[0] *= uniform; s[1] *= uniform; s[2] *= uniform; s[3] *= uniform; }
+    if (add != nullptr) {
+      float a[4];
+      load_floats<TA, 4>(add + t * width + c, a);
+      s[0] += a[0]; s[1] += a[1]; s[2] += a[2]; s[3] += a[3];
+    }
+    *reinterpret_cast<float4*>(out + t * width + c) = make_float4(s[0], s[1], s[2], s[3]);
+    return;
+  }
+  for (int c = blockIdx.y * 1024 + threadIdx.x; c < min(width, (static_cast<int>(blockIdx.y) + 1) * 1024); c += blockDim.x) {
     float s = 0.0f;
     if (weight == nullptr) {
       for (int k = 0; k < top; ++k) s += Y[static_cast<size_t>(pos_of_pair[t * top + k]) * width + c];
@@ -475,11 +499,12 @@ struct ExpertChoice {
 static int launch_combine(float* out, const float* y, const int* pos_of_pair, int tokens, int top, int width,
                           const ExpertChoice& c, cudaStream_t stream) {
   const float uniform = 1.0f / static_cast<float>(top);
+  const dim3 combine_grid(tokens, (width + 1023) / 1024);
   if (c.add != nullptr && c.add_dtype == B200_BF16)
-    expert_combine_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(out, y, pos_of_pair, top, width, uniform, c.weight,
+    expert_combine_kernel<__nv_bfloat16><<<combine_grid, 256, 0, stream>>>(out, y, pos_of_pair, top, width, uniform, c.weight,
                                                                      static_cast<const __nv_bfloat16*>(c.add));
   else
-    expert_combine_kernel<float><<<tokens, 256, 0, stream>>>(out, y, pos_of_pair, top, width, uniform, c.weight,
+    expert_combine_kernel<float><<<combine_grid, 256, 0, stream>>>(out, y, pos_of_pair, top, width, uniform, c.weight,
                                                              static_cast<const float*>(c.add));
   return b200_check_launch();
 }

@@ -11,7 +11,11 @@
 //
 // `g` is a column range of a wider matrix (row stride g_stride), so a gate that was projected together with
 // other things is read where it lies.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -386,78 +390,71 @@ B200_EXPORT int b200_act_table_mul(void* out, const void* z, const void* table, 
   return b200_check_launch();
 }
 
-// The whole gated read of a second token table for a step of few tokens, one block a token, where four launches
-// would each move a few kilobytes:
+// The whole gated read of a second token table for a step of few tokens, one cluster of SIDE_CLUSTER blocks a token,
+// where four launches would each move a few kilobytes:
 //   z = Wg x (rounded to T);  g = act(z) * table[id][column ..] (rounded to T);  y = Wp g (float)
 //   stream <- stream + y / sqrt(mean(y^2) + eps) * norm;   cast_out <- the new stream rounded to T (if given)
-// x [tokens, width] is the stream rounded to T (the stream itself in float32; it is read before it is written).
-// Wg [dim, width], Wp [width, dim].  A warp takes four rows of Wg at a time, its lanes eight columns each and then 256
-// further on, in order; a thread takes a row of Wp.  Shared memory: dim + width floats.
-constexpr int SIDE_THREADS = 512;
+// x [tokens, width] is the stream rounded to T (the stream itself in float32: every block has read it before the
+// first barrier of the cluster, and writes come after the second).  Wg [dim, width], Wp [width, dim].
+// Block r of the cluster takes rows r, r + SIDE_CLUSTER, .. of Wg (a warp a row, its lanes eight columns each and
+// then 256 further on, in order) and sends each g to every block's shared memory; then it takes its slice of the
+// columns of y (a thread a row of Wp), sends its part of the sum of squares to every block, and all add the parts in
+// the order of the blocks.  Shared memory: dim + slice floats.
+constexpr int SIDE_THREADS = 256, SIDE_CLUSTER = 8;
 
 template <typename T>
 __global__ void __launch_bounds__(SIDE_THREADS)
 token_side_few_kernel(float* stream, const T* x, const T* __restrict__ gate, const T* __restrict__ table,
                       const int* __restrict__ ids, const T* __restrict__ proj, const float* __restrict__ norm_w,
                       float eps, T* __restrict__ cast_out, int vocab, int table_width, int column, int dim, int width,
-                      int act, int* err) {
-  __shared__ float part[SIDE_THREADS / 32];
+                      int slice, int act, int* err) {
+  constexpr int NW = SIDE_THREADS / 32;
+  __shared__ float warp_part[NW];
+  __shared__ float part[SIDE_CLUSTER];
   extern __shared__ float side_sm[];
   float* g = side_sm;                                // dim
-  float* y = side_sm + dim;                          // width
-  const size_t t = blockIdx.x;
+  float* y = side_sm + dim;                          // slice
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = static_cast<int>(cluster.block_rank());
+  const size_t t = blockIdx.x / SIDE_CLUSTER;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   int id = ids[t];
   if (id < 0 || id >= vocab) {
-    if (threadIdx.x == 0) atomicOr(err, B200_ERR_TOKEN_RANGE);
+    if (threadIdx.x == 0 && rank == 0) atomicOr(err, B200_ERR_TOKEN_RANGE);
     id = 0;
   }
   const T* e = table + static_cast<size_t>(id) * table_width + column;
   const T* xr = x + t * width;
   const bool wide = width % 8 == 0;
-  constexpr int NW = SIDE_THREADS / 32;
-  for (int jb = 0; jb < dim; jb += 4 * NW) {         // four rows of Wg a warp at a time: one read of x serves them all
-    const T* w[4];
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-    for (int r = 0; r < 4; ++r) w[r] = gate + static_cast<size_t>(min(jb + warp + r * NW, dim - 1)) * width;
+  cluster.sync();                                    // every block of the cluster runs: its shared memory can be written
+  for (int j = rank + SIDE_CLUSTER * warp; j < dim; j += SIDE_CLUSTER * NW) {
+    const T* w = gate + static_cast<size_t>(j) * width;
+    float acc = 0.0f;
     if (wide) {
-#pragma unroll 2
+#pragma unroll 4
       for (int k = lane * 8; k < width; k += 256) {
-        float b[8];
+        float a[8], b[8];
+        load_floats<T, 8>(w + k, a);
         load_floats<T, 8>(xr + k, b);
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          float a[8];
-          load_floats<T, 8>(w[r] + k, a);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) acc[r] = fmaf(a[i], b[i], acc[r]);
-        }
+        for (int i = 0; i < 8; ++i) acc = fmaf(a[i], b[i], acc);
       }
     } else {
       for (int k8 = lane * 8; k8 < width; k8 += 256) {
         const int end = min(k8 + 8, width);
-        for (int k = k8; k < end; ++k) {
-          const float b = to_f32<T>(xr[k]);
-#pragma unroll
-          for (int r = 0; r < 4; ++r) acc[r] = fmaf(to_f32<T>(w[r][k]), b, acc[r]);
-        }
+        for (int k = k8; k < end; ++k) acc = fmaf(to_f32<T>(w[k]), to_f32<T>(xr[k]), acc);
       }
     }
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const float sum = warp_sum(acc[r]);
-      const int j = jb + warp + r * NW;
-      if (lane == 0 && j < dim) {
-        const float z = to_f32<T>(from_f32<T>(sum));
-        g[j] = to_f32<T>(from_f32<T>(activate(z, act) * to_f32<T>(e[j])));
-      }
-    }
+    acc = warp_sum(acc);
+    const float z = to_f32<T>(from_f32<T>(acc));
+    const float gj = to_f32<T>(from_f32<T>(activate(z, act) * to_f32<T>(e[j])));
+    if (lane < SIDE_CLUSTER) *cluster.map_shared_rank(&g[j], lane) = gj;
   }
-  __syncthreads();
+  cluster.sync();
+  const int lo = rank * slice, hi = min(width, lo + slice);
   float ss = 0.0f;
   const bool wide_dim = dim % 8 == 0;
-  for (int c = threadIdx.x; c < width; c += SIDE_THREADS) {
+  for (int c = lo + threadIdx.x; c < hi; c += SIDE_THREADS) {
     const T* w = proj + static_cast<size_t>(c) * dim;
     float acc = 0.0f;
     if (wide_dim) {
@@ -471,19 +468,26 @@ token_side_few_kernel(float* stream, const T* x, const T* __restrict__ gate, con
     } else {
       for (int k = 0; k < dim; ++k) acc = fmaf(to_f32<T>(w[k]), g[k], acc);
     }
-    y[c] = acc;
+    y[c - lo] = acc;
     ss = fmaf(acc, acc, ss);
   }
   ss = warp_sum(ss);
-  if (lane == 0) part[warp] = ss;
+  if (lane == 0) warp_part[warp] = ss;
   __syncthreads();
+  if (threadIdx.x < SIDE_CLUSTER) {
+    float mine = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NW; ++i) mine += warp_part[i];
+    *cluster.map_shared_rank(&part[rank], threadIdx.x) = mine;
+  }
+  cluster.sync();
   ss = 0.0f;
 #pragma unroll
-  for (int i = 0; i < SIDE_THREADS / 32; ++i) ss += part[i];
+  for (int i = 0; i < SIDE_CLUSTER; ++i) ss += part[i];
   const float r = 1.0f / sqrtf(ss / static_cast<float>(width) + eps);
   float* sr = stream + t * width;
-  for (int c = threadIdx.x; c < width; c += SIDE_THREADS) {
-    const float s = sr[c] + y[c] * r * norm_w[c];
+  for (int c = lo + threadIdx.x; c < hi; c += SIDE_THREADS) {
+    const float s = sr[c] + y[c - lo] * r * norm_w[c];
     sr[c] = s;
     if (cast_out != nullptr) cast_out[t * width + c] = from_f32<T>(s);
   }
@@ -498,8 +502,21 @@ B200_EXPORT int b200_token_side_few(float* stream, const void* x, const void* ga
   if (act < ACT_SILU || act > ACT_RELU_SQUARED || vocab <= 0 || dim <= 0 || width <= 0 || column < 0 ||
       column + dim > table_width)
     return B200_BAD_SIZE;
-  const size_t smem = (static_cast<size_t>(dim) + width) * sizeof(float);
+  const int slice = (width + SIDE_CLUSTER - 1) / SIDE_CLUSTER;
+  const size_t smem = (static_cast<size_t>(dim) + slice) * sizeof(float);
   if (smem > 200 * 1024) return B200_BAD_SIZE;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(tokens * SIDE_CLUSTER);
+  config.blockDim = dim3(SIDE_THREADS);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream_;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = SIDE_CLUSTER;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
 #define B200_SIDE(T)                                                                                               \
   do {                                                                                                             \
     if (smem > 48 * 1024) {                                                                                        \
@@ -507,10 +524,11 @@ B200_EXPORT int b200_token_side_few(float* stream, const void* x, const void* ga
                                            static_cast<int>(smem));                                                \
       if (e != cudaSuccess) return static_cast<int>(e);                                                            \
     }                                                                                                              \
-    token_side_few_kernel<T><<<tokens, SIDE_THREADS, smem, stream_>>>(                                             \
-        stream, static_cast<const T*>(x), static_cast<const T*>(gate), static_cast<const T*>(table), ids,          \
-        static_cast<const T*>(proj), norm_w, eps, static_cast<T*>(cast_out), vocab, table_width, column, dim,      \
-        width, act, err);                                                                                          \
+    cudaError_t e = cudaLaunchKernelEx(&config, token_side_few_kernel<T>, stream, static_cast<const T*>(x),        \
+                                       static_cast<const T*>(gate), static_cast<const T*>(table), ids,             \
+                                       static_cast<const T*>(proj), norm_w, eps, static_cast<T*>(cast_out), vocab, \
+                                       table_width, column, dim, width, slice, act, err);                          \
+    if (e != cudaSuccess) return static_cast<int>(e);                                                              \
   } while (0)
   if (dtype == B200_F32) B200_SIDE(float);
   else if (dtype == B200_BF16) B200_SIDE(__nv_bfloat16);

@@ -11,17 +11,57 @@
 // not depend on what else is in the step.
 #include "common.cuh"
 
-constexpr int PN_THREADS = 256;
+constexpr int PN_THREADS = 256, PN_MAX_THREADS = 1024;
 
+template <typename T> __device__ __forceinline__ void store4(T* p, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float a, float b, float c, float d) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 v;
+  v.x = *reinterpret_cast<const uint32_t*>(&lo);
+  v.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = v;
+}
+
+// Up to PN_MAX_THREADS threads a block (the launcher gives a step of few tokens more threads each); a width that is a
+// multiple of four is taken four columns at a time.
 template <typename TY, typename TO>
-__global__ void __launch_bounds__(PN_THREADS)
+__global__ void __launch_bounds__(PN_MAX_THREADS)
 norm_add_kernel(float* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ bias,
                 const float* __restrict__ w, float eps, TO* __restrict__ cast_out, int width) {
   __shared__ float scratch[33];
   extern __shared__ float row[];                     // width floats: y + bias
   const size_t t = blockIdx.x;
   const TY* src = y + t * width;
+  float* xr = x + t * width;
   float ss = 0.0f;
+  if (width % 4 == 0) {
+#pragma unroll 2
+    for (int c = 4 * threadIdx.x; c < width; c += 4 * blockDim.x) {
+      float v[4];
+      load_floats<TY, 4>(src + c, v);
+      if (bias != nullptr) {
+        const float4 b = *reinterpret_cast<const float4*>(bias + c);
+        v[0] += b.x; v[1] += b.y; v[2] += b.z; v[3] += b.w;
+      }
+      *reinterpret_cast<float4*>(row + c) = make_float4(v[0], v[1], v[2], v[3]);
+      ss = fmaf(v[0], v[0], ss); ss = fmaf(v[1], v[1], ss); ss = fmaf(v[2], v[2], ss); ss = fmaf(v[3], v[3], ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(ss / static_cast<float>(width) + eps);
+#pragma unroll 2
+    for (int c = 4 * threadIdx.x; c < width; c += 4 * blockDim.x) {
+      const float4 a = *reinterpret_cast<const float4*>(xr + c);
+      const float4 g = *reinterpret_cast<const float4*>(w + c);
+      const float4 v = *reinterpret_cast<const float4*>(row + c);
+      const float s0 = a.x + v.x * r * g.x, s1 = a.y + v.y * r * g.y, s2 = a.z + v.z * r * g.z, s3 = a.w + v.w * r * g.w;
+      *reinterpret_cast<float4*>(xr + c) = make_float4(s0, s1, s2, s3);
+      if (cast_out != nullptr) store4<TO>(cast_out + t * width + c, s0, s1, s2, s3);
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     float v = to_f32<TY>(src[c]);
     if (bias != nullptr) v += bias[c];
@@ -30,7 +70,6 @@ norm_add_kernel(float* __restrict__ x, const TY* __restrict__ y, const float* __
   }
   ss = block_sum(ss, scratch);
   const float r = 1.0f / sqrtf(ss / static_cast<float>(width) + eps);
-  float* xr = x + t * width;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     const float s = xr[c] + row[c] * r * w[c];
     xr[c] = s;
@@ -59,6 +98,8 @@ B200_EXPORT int b200_norm_add(float* x, const void* y, int y_dtype, const float*
   if (tokens <= 0) return 0;
   if (width <= 0 || width * sizeof(float) > 200 * 1024) return B200_BAD_SIZE;
   const size_t smem = static_cast<size_t>(width) * sizeof(float);
+  // a step of few tokens: as many threads a block as the row has groups of four columns, up to PN_MAX_THREADS
+  const int threads = tokens <= 64 ? min(PN_MAX_THREADS, max(PN_THREADS, (width / 4 + 31) / 32 * 32)) : PN_THREADS;
 #define B200_NORM_ADD(TY, TO)                                                                                  \
   do {                                                                                                         \
     if (smem > 48 * 1024) {                                                                                    \
@@ -66,8 +107,8 @@ B200_EXPORT int b200_norm_add(float* x, const void* y, int y_dtype, const float*
                                            static_cast<int>(smem));                                            \
       if (e != cudaSuccess) return static_cast<int>(e);                                                        \
     }                                                                                                          \
-    norm_add_kernel<TY, TO><<<tokens, PN_THREADS, smem, stream>>>(x, static_cast<const TY*>(y), bias, w, eps,   \
-                                                                  static_cast<TO*>(cast_out), width);          \
+    norm_add_kernel<TY, TO><<<tokens, threads, smem, stream>>>(x, static_cast<const TY*>(y), bias, w, eps,      \
+                                                               static_cast<TO*>(cast_out), width);             \
   } while (0)
   const bool to_bf16 = cast_out != nullptr && out_dtype == B200_BF16;
   if (cast_out != nullptr && out_dtype != B200_BF16 && out_dtype != B200_F32) return B200_BAD_DTYPE;
