@@ -358,6 +358,29 @@ def test_whole_decoded_and_in_portions(name, dtype, models):
     assert eng.cache.manager.check() == ""
 
 
+@pytest.mark.parametrize("dim,vdim,heads,kv", [(24, 24, 3, 1), (80, 80, 4, 2), (96, 96, 2, 1), (128, 128, 4, 2),
+                                               (256, 256, 2, 1), (128, 64, 2, 2)])
+def test_head_sizes_of_every_kernel_family(dim, vdim, heads, kv, tmp_path):
+    """Head sizes beyond the fixed configurations': multiples of 16 up to 256 (tensor-core kernels in bfloat16), one
+    that is none, and values narrower than keys; two layers, the second on the first one's keys, whole, decoded and in
+    portions."""
+    raw = K.config(83, 64, 1e-5, [
+        K.attention(heads, kv, dim, vdim, dim ** -0.5, 40, (10000.0, dim - 8), mlp=K.dense(48)),
+        K.attention(heads, kv, dim, vdim, 0.9 * dim ** -0.5, 23, (10000.0, dim - 8), kv_from=0)], side=4)
+    T = 130
+    ids = K.tokens(raw["vocab"], T, dim)
+    w = K.random_weights(raw, 900 + dim)
+    folder = K.write_model(str(tmp_path / "m"), raw, w)
+    want, close = K.oracle_and_close_calls(raw, w, ids)
+    for dtype in ("float32", "bfloat16"):
+        eng = K.make_engine(folder, dtype, page_size=16, pool_tokens=256)
+        K.check_clear(K.run_alone(eng, 1, ids, [T]), want, close, dtype, "whole")
+        K.check_clear(K.run_alone(eng, 2, ids, [T - 50] + [1] * 50), want, close, dtype, "last 50 decoded")
+        K.check_clear(K.run_alone(eng, 3, ids, cut(T, [33, 2, 64, 7])), want, close, dtype, "in portions")
+        eng.check_kernel_errors()
+        del eng
+
+
 def test_every_layer_against_the_plain_stream(models):
     """The float32 stream after every layer, whole and cut into portions."""
     from llm_infer_rust_b200.engine import StepEntry
