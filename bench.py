@@ -812,6 +812,13 @@ def torinex_kernel_table(size, peak):
         ids = torch.randint(0, 4096, (T,), device=dev, dtype=torch.int32)
         put(f"{phase}.torinex.act_table_mul", timed_alone(lambda: ops.act_table_mul(zs, "gelu_tanh", table2, ids, 3 * side),
                                                           flush), T * side * 6)
+        if phase == "decode":                                      # the whole read in one kernel for a step of few tokens
+            sg = (torch.randn(side, W, device=dev) * W ** -0.5).to(bf)
+            sp = torch.randn(W, side, device=dev).to(bf)
+            xs = stream.to(bf)
+            put("decode.torinex.token_side_few", timed_alone(lambda: ops.token_side_few(
+                stream, xs, sg, table2, ids, 3 * side, sp, wn, 1e-5, "gelu_tanh", cast_to=bf), flush),
+                2 * side * W * 2 + T * W * 14)
         # --- router and experts beside Mukenex's experts and Qwen3's feed-forward with the same active parameters
         xe = torch.randn(T, W, device=dev).to(bf)
         wr = (torch.randn(E, W, device=dev) * W ** -0.5).to(bf)
@@ -902,7 +909,7 @@ def main() -> int:
                     help="run one phase alone and print a short line (for profiling)")
     ap.add_argument("--design", choices=["qwen3", "kefetar", "mukenex", "torinex"], default="qwen3",
                     help="kefetar, mukenex, torinex: that design beside Qwen3 at equal sizes, and its kernels alone (another line)")
-    ap.add_argument("--design-sizes", default="1k,4k", help="layer sizes of --design kefetar / mukenex, comma separated")
+    ap.add_argument("--design-sizes", default="1k,4k", help="layer sizes of --design kefetar / mukenex / torinex, comma separated")
     ap.add_argument("--no-kernels", action="store_true", help="--design ... without the table of single kernels")
     args = ap.parse_args()
     if args.design in DESIGNS and args.impl == "ours":
