@@ -16,7 +16,8 @@
 // Weights: gate_up [experts, 2 * ff, width] (an expert's gate rows, then its up rows), down [experts, width, ff].
 // float32: FFMA, every output accumulated over k in order (a pair's result does not depend on its place in a tile,
 // so the order in which pairs of one expert were sorted does not show).  bfloat16: tensor cores with float
-// accumulation, H rounded once to bfloat16.
+// accumulation, H rounded once to bfloat16; a step of at most 64 pairs (a decode step) takes expert_rows_few_kernel
+// instead, which streams every weight row once for the few rows that need it.
 #include <mma.h>
 
 #include "common.cuh"
@@ -271,6 +272,65 @@ expert_gemm_bf16_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int*
     const int r = r0 + wr * 16 + rr, n = n0 + wc * 32 + cc;
     if (r >= r_end || n >= N) continue;
     C[static_cast<size_t>(r) * N + n] = from_f32<TO>(Cs[warp][rr][cc]);
+  }
+}
+
+// ------------------------------------------------------------------ bfloat16 products of a step of few pairs
+// A decode step has a handful of rows an expert and must read all of that expert's weights: the tensor cores have
+// nothing to do, and the time is the weights' way out of memory.  So each warp takes ONE output column n of ONE
+// expert (its gate row and its up row when GATED), streams the rows in 16-byte pieces (lane l takes columns
+// 8 l .. 8 l + 7, then 256 further on, in order; the lanes' sums meet in a butterfly) and multiplies them with up to
+// FEW_ROWS of the expert's rows at a time (more rows: another pass over the same weight rows, which the caches still
+// hold).  grid (ceil(N / FEW_WARPS), experts); blocks of experts without rows return at once.  A row's result does
+// not depend on what else the step holds.  K a multiple of 8.
+constexpr int FEW_PAIRS = 64, FEW_ROWS = 4, FEW_WARPS = 8;
+
+template <bool GATED, typename TO>
+__global__ void __launch_bounds__(FEW_WARPS * 32)
+expert_rows_few_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int* __restrict__ sorted_token,
+                       const __nv_bfloat16* __restrict__ W, long long w_stride, int ff, TO* __restrict__ C, int ldc,
+                       int N, int K, const int* __restrict__ expert_start, const GluAct act) {
+  const int e = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n = blockIdx.x * FEW_WARPS + warp;
+  const int first = expert_start[e], last = expert_start[e + 1];
+  if (first >= last || n >= N) return;
+  const __nv_bfloat16* w0 = W + static_cast<size_t>(e) * w_stride + static_cast<size_t>(n) * K;
+  const __nv_bfloat16* w1 = GATED ? w0 + static_cast<size_t>(ff) * K : w0;
+  for (int r0 = first; r0 < last; r0 += FEW_ROWS) {
+    const int nr = min(FEW_ROWS, last - r0);
+    const __nv_bfloat16* a[FEW_ROWS];
+#pragma unroll
+    for (int i = 0; i < FEW_ROWS; ++i) {             // a row beyond the last reads the last one; its sums are dropped
+      const int r = r0 + min(i, nr - 1);
+      a[i] = A + static_cast<size_t>(GATED ? sorted_token[r] : r) * lda;
+    }
+    float acc0[FEW_ROWS], acc1[FEW_ROWS];
+#pragma unroll
+    for (int i = 0; i < FEW_ROWS; ++i) acc0[i] = acc1[i] = 0.0f;
+#pragma unroll 2
+    for (int k = lane * 8; k < K; k += 256) {
+      float g[8], u[8];
+      load_floats<__nv_bfloat16, 8>(w0 + k, g);
+      if (GATED) load_floats<__nv_bfloat16, 8>(w1 + k, u);
+#pragma unroll
+      for (int i = 0; i < FEW_ROWS; ++i) {
+        float v[8];
+        load_floats<__nv_bfloat16, 8>(a[i] + k, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          acc0[i] = fmaf(g[j], v[j], acc0[i]);
+          if (GATED) acc1[i] = fmaf(u[j], v[j], acc1[i]);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < FEW_ROWS; ++i) {
+      const float s0 = warp_sum(acc0[i]);
+      const float s1 = GATED ? warp_sum(acc1[i]) : 0.0f;
+      if (lane == 0 && i < nr)
+        C[static_cast<size_t>(r0 + i) * ldc + n] = from_f32<TO>(GATED ? glu_f(s0, s1, act) : s0);
+    }
   }
 }
 
@@ -538,6 +598,14 @@ static int run_experts(const void* x, int dtype, const ExpertChoice& c, int top,
     expert_gemm_f32_kernel<false><<<g2, 256, 0, stream>>>(
         static_cast<const float*>(h), ff, nullptr, static_cast<const float*>(down), dn_stride, 0, y, width, ff,
         expert_start, tile_expert, tile_first, num_tiles, act);
+  } else if (dtype == B200_BF16 && pairs <= FEW_PAIRS && width % 8 == 0 && ff % 8 == 0) {
+    const dim3 f1((ff + FEW_WARPS - 1) / FEW_WARPS, experts), f2((width + FEW_WARPS - 1) / FEW_WARPS, experts);
+    expert_rows_few_kernel<true, __nv_bfloat16><<<f1, FEW_WARPS * 32, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), width, sorted_token, static_cast<const __nv_bfloat16*>(gate_up),
+        gu_stride, ff, static_cast<__nv_bfloat16*>(h), ff, ff, width, expert_start, act);
+    expert_rows_few_kernel<false, float><<<f2, FEW_WARPS * 32, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(h), ff, nullptr, static_cast<const __nv_bfloat16*>(down), dn_stride, 0, y,
+        width, width, ff, expert_start, act);
   } else if (dtype == B200_BF16) {
     expert_gemm_bf16_kernel<true, __nv_bfloat16><<<g1, 256, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(x), width, sorted_token, static_cast<const __nv_bfloat16*>(gate_up),
