@@ -170,6 +170,8 @@ joint_heads_prepare_kernel(const T* __restrict__ x, int in_stride, const float* 
                            const int* __restrict__ positions, const int* __restrict__ slots, int nh, int nkv, int d,
                            int dv, int has_kv, int page_size, long long cache_slots, T* __restrict__ q_out,
                            T* __restrict__ k_cache, T* __restrict__ v_cache, int* err) {
+  pdl_launch_dependents();                          // the kernel after this one may be scheduled; it waits before it reads
+  pdl_wait();                                        // what this kernel reads belongs to the kernels before it
   __shared__ float sums[2][32];
   extern __shared__ float jrow[];                    // q (nh * d), then k (nkv * d), then v (nkv * dv), then cos, sin
   const int t = blockIdx.x;
@@ -363,10 +365,11 @@ B200_EXPORT int b200_joint_heads_prepare(const void* x, int dtype, int in_stride
                                            static_cast<int>(smem));                                                 \
       if (e != cudaSuccess) return static_cast<int>(e);                                                             \
     }                                                                                                               \
-    joint_heads_prepare_kernel<T><<<tokens, threads, smem, stream>>>(                                                   \
+    const int rc = b200_launch(joint_heads_prepare_kernel<T>, dim3(tokens), dim3(threads), smem, stream, 0,          \
         static_cast<const T*>(x), in_stride, bias, q_w, k_w, eps, inv_freq, rot_dims, interleaved, positions, slots, \
         nh, nkv, d, dv, has_kv, page_size, cache_slots, static_cast<T*>(q_out), static_cast<T*>(k_cache),           \
         static_cast<T*>(v_cache), err);                                                                             \
+    if (rc != 0) return rc;                                                                                         \
   } while (0)
   if (dtype == B200_F32) B200_JOINT(float);
   else if (dtype == B200_BF16) B200_JOINT(__nv_bfloat16);

@@ -40,6 +40,8 @@ expert_route_kernel(const int* __restrict__ token_ids, const int* __restrict__ t
                     const int* __restrict__ choice, int tokens, int* __restrict__ sorted_token, int* __restrict__ pos_of_pair,
                     int* __restrict__ expert_start, int* __restrict__ tile_expert, int* __restrict__ tile_first,
                     int* __restrict__ num_tiles, int tile_rows, int* err) {
+  pdl_launch_dependents();                          // the kernel after this one may be scheduled; it waits before it reads
+  pdl_wait();                                        // what this kernel reads belongs to the kernels before it
   extern __shared__ int sm[];
   int* count = sm;                    // [experts]
   int* start = sm + experts;          // [experts + 1]
@@ -290,6 +292,8 @@ __global__ void __launch_bounds__(FEW_WARPS * 32)
 expert_rows_few_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int* __restrict__ sorted_token,
                        const __nv_bfloat16* __restrict__ W, long long w_stride, int ff, TO* __restrict__ C, int ldc,
                        int N, int K, const int* __restrict__ expert_start, const GluAct act) {
+  pdl_launch_dependents();                          // the kernel after this one may be scheduled; it waits before it reads
+  pdl_wait();                                        // what this kernel reads belongs to the kernels before it
   const int e = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int n = blockIdx.x * FEW_WARPS + warp;
@@ -343,6 +347,8 @@ __global__ void __launch_bounds__(256)
 expert_combine_kernel(float* __restrict__ out, const float* __restrict__ Y, const int* __restrict__ pos_of_pair,
                       int top, int width, float uniform, const float* __restrict__ weight,
                       const TA* __restrict__ add) {
+  pdl_launch_dependents();                          // the kernel after this one may be scheduled; it waits before it reads
+  pdl_wait();                                        // what this kernel reads belongs to the kernels before it
   const size_t t = blockIdx.x;
   if (width % 4 == 0) {
     const int c = (blockIdx.y * 256 + threadIdx.x) * 4;
@@ -397,6 +403,8 @@ __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 expert_router_kernel(const TX* __restrict__ x, const TW* __restrict__ W, int tokens, int width, int experts,
                      int groups, int keep, int top, int sigmoid_scores, int renormalize, int* __restrict__ choice,
                      float* __restrict__ weight) {
+  pdl_launch_dependents();                          // the kernel after this one may be scheduled; it waits before it reads
+  pdl_wait();                                        // what this kernel reads belongs to the kernels before it
   extern __shared__ float rsm[];
   float* z = rsm;                                                   // [TT][experts]
   int* open = reinterpret_cast<int*>(rsm + TT * experts);           // [TT][experts]: may still be chosen
@@ -561,12 +569,10 @@ static int launch_combine(float* out, const float* y, const int* pos_of_pair, in
   const float uniform = 1.0f / static_cast<float>(top);
   const dim3 combine_grid(tokens, (width + 1023) / 1024);
   if (c.add != nullptr && c.add_dtype == B200_BF16)
-    expert_combine_kernel<__nv_bfloat16><<<combine_grid, 256, 0, stream>>>(out, y, pos_of_pair, top, width, uniform, c.weight,
-                                                                     static_cast<const __nv_bfloat16*>(c.add));
-  else
-    expert_combine_kernel<float><<<combine_grid, 256, 0, stream>>>(out, y, pos_of_pair, top, width, uniform, c.weight,
-                                                             static_cast<const float*>(c.add));
-  return b200_check_launch();
+    return b200_launch(expert_combine_kernel<__nv_bfloat16>, combine_grid, dim3(256), 0, stream, 0, out, y, pos_of_pair,
+                       top, width, uniform, c.weight, static_cast<const __nv_bfloat16*>(c.add));
+  return b200_launch(expert_combine_kernel<float>, combine_grid, dim3(256), 0, stream, 0, out, y, pos_of_pair, top, width,
+                     uniform, c.weight, static_cast<const float*>(c.add));
 }
 
 // x [tokens, width] -> out [tokens, width] float32.  `h` holds pairs * ff elements of x's dtype, `y` pairs * width
@@ -584,10 +590,9 @@ static int run_experts(const void* x, int dtype, const ExpertChoice& c, int top,
   if (tiles > 65535) return B200_BAD_SIZE;
   int *sorted_token = rl.sorted_token, *pos_of_pair = rl.pos_of_pair, *expert_start = rl.expert_start;
   int *tile_expert = rl.tile_expert, *tile_first = rl.tile_first, *num_tiles = rl.num_tiles;
-  expert_route_kernel<<<1, 1024, (2 * experts + 1) * sizeof(int), stream>>>(
-      c.token_ids, c.table, c.vocab, top, experts, c.choice, tokens, sorted_token, pos_of_pair, expert_start,
-      tile_expert, tile_first, num_tiles, TM, err);
-  int rc = b200_check_launch();
+  int rc = b200_launch(expert_route_kernel, dim3(1), dim3(1024), (2 * experts + 1) * sizeof(int), stream, 0,
+                       c.token_ids, c.table, c.vocab, top, experts, c.choice, tokens, sorted_token, pos_of_pair,
+                       expert_start, tile_expert, tile_first, num_tiles, TM, err);
   if (rc != 0) return rc;
   const dim3 g1((ff + TN - 1) / TN, tiles), g2((width + TN - 1) / TN, tiles);
   const long long gu_stride = 2ll * ff * width, dn_stride = static_cast<long long>(width) * ff;
@@ -600,12 +605,14 @@ static int run_experts(const void* x, int dtype, const ExpertChoice& c, int top,
         expert_start, tile_expert, tile_first, num_tiles, act);
   } else if (dtype == B200_BF16 && pairs <= FEW_PAIRS && width % 8 == 0 && ff % 8 == 0) {
     const dim3 f1((ff + FEW_WARPS - 1) / FEW_WARPS, experts), f2((width + FEW_WARPS - 1) / FEW_WARPS, experts);
-    expert_rows_few_kernel<true, __nv_bfloat16><<<f1, FEW_WARPS * 32, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(x), width, sorted_token, static_cast<const __nv_bfloat16*>(gate_up),
-        gu_stride, ff, static_cast<__nv_bfloat16*>(h), ff, ff, width, expert_start, act);
-    expert_rows_few_kernel<false, float><<<f2, FEW_WARPS * 32, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(h), ff, nullptr, static_cast<const __nv_bfloat16*>(down), dn_stride, 0, y,
-        width, width, ff, expert_start, act);
+    rc = b200_launch(expert_rows_few_kernel<true, __nv_bfloat16>, f1, dim3(FEW_WARPS * 32), 0, stream, 0,
+                     static_cast<const __nv_bfloat16*>(x), width, sorted_token, static_cast<const __nv_bfloat16*>(gate_up),
+                     gu_stride, ff, static_cast<__nv_bfloat16*>(h), ff, ff, width, expert_start, act);
+    if (rc != 0) return rc;
+    rc = b200_launch(expert_rows_few_kernel<false, float>, f2, dim3(FEW_WARPS * 32), 0, stream, 0,
+                     static_cast<const __nv_bfloat16*>(h), ff, static_cast<const int*>(nullptr),
+                     static_cast<const __nv_bfloat16*>(down), dn_stride, 0, y, width, width, ff, expert_start, act);
+    if (rc != 0) return rc;
   } else if (dtype == B200_BF16) {
     expert_gemm_bf16_kernel<true, __nv_bfloat16><<<g1, 256, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(x), width, sorted_token, static_cast<const __nv_bfloat16*>(gate_up),
@@ -642,8 +649,9 @@ B200_EXPORT int b200_expert_router(const void* x, int x_dtype, const void* w, in
   const size_t smem = static_cast<size_t>(per_block) * experts * (sizeof(float) + sizeof(int));
   if (static_cast<size_t>(8) * experts * (sizeof(float) + sizeof(int)) > 48 * 1024) return B200_BAD_SIZE;
   const unsigned blocks = (tokens + per_block - 1) / per_block;
+  int router_rc = 0;
 #define B200_ROUTER_TT(TX, TW, TT)                                                                                   \
-  expert_router_kernel<TX, TW, TT><<<blocks, ROUTER_WARPS * 32, smem, stream>>>(                                     \
+  router_rc = b200_launch(expert_router_kernel<TX, TW, TT>, dim3(blocks), dim3(ROUTER_WARPS * 32), smem, stream, 0,  \
       static_cast<const TX*>(x), static_cast<const TW*>(w), tokens, width, experts, groups, keep, top, sigmoid_scores, \
       renormalize, choice, weight)
 #define B200_ROUTER(TX, TW)                                                                                          \
@@ -658,7 +666,7 @@ B200_EXPORT int b200_expert_router(const void* x, int x_dtype, const void* w, in
   else return B200_BAD_DTYPE;
 #undef B200_ROUTER_TT
 #undef B200_ROUTER
-  return b200_check_launch();
+  return router_rc;
 }
 
 // Experts chosen by a router: choice and weight [tokens, top] (b200_expert_router), glu kind `act_kind` with `limit`

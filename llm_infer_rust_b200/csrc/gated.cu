@@ -215,6 +215,8 @@ __device__ __forceinline__ float activate(float z, int act) {
 template <typename T>
 __global__ void __launch_bounds__(256)
 activate_columns_kernel(T* out, int out_stride, const T* x, int stride, int columns, int act) {   // out may be x
+  pdl_launch_dependents();                          // the kernel after this one may be scheduled; it waits before it reads
+  pdl_wait();                                        // what this kernel reads belongs to the kernels before it
   const size_t t = blockIdx.x;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c < columns) out[t * out_stride + c] = from_f32<T>(activate(to_f32<T>(x[t * stride + c]), act));
@@ -224,6 +226,8 @@ activate_columns_kernel(T* out, int out_stride, const T* x, int stride, int colu
 template <typename T>
 __global__ void __launch_bounds__(256)
 activate_columns_vec_kernel(T* out, int out_stride, const T* x, int stride, int columns, int act) {
+  pdl_launch_dependents();                          // the kernel after this one may be scheduled; it waits before it reads
+  pdl_wait();                                        // what this kernel reads belongs to the kernels before it
   const size_t t = blockIdx.x;
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   if (c >= columns) return;
@@ -270,29 +274,30 @@ __global__ void __launch_bounds__(256) tanh_cap_kernel(float* z, long long n, fl
 
 B200_EXPORT int b200_activate_columns(void* out, int out_stride, const void* x, int stride, int tokens, int columns,
                                       int act, int dtype, cudaStream_t stream) {
+  int launch_rc = 0;
   if (tokens <= 0 || columns <= 0) return 0;
   if (act < ACT_SILU || act > ACT_RELU_SQUARED || stride < columns || out_stride < columns) return B200_BAD_SIZE;
   if (columns % 8 == 0 && stride % 8 == 0 && out_stride % 8 == 0 && (dtype == B200_F32 || dtype == B200_BF16) &&
       (reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(x)) % 32 == 0) {
     const dim3 vgrid(tokens, (columns / 8 + 255) / 256);
     if (dtype == B200_F32)
-      activate_columns_vec_kernel<float><<<vgrid, 256, 0, stream>>>(static_cast<float*>(out), out_stride,
+      launch_rc = b200_launch(activate_columns_vec_kernel<float>, dim3(vgrid), dim3(256), 0, stream, 0, static_cast<float*>(out), out_stride,
                                                                     static_cast<const float*>(x), stride, columns, act);
     else
-      activate_columns_vec_kernel<__nv_bfloat16><<<vgrid, 256, 0, stream>>>(
+      launch_rc = b200_launch(activate_columns_vec_kernel<__nv_bfloat16>, dim3(vgrid), dim3(256), 0, stream, 0, 
           static_cast<__nv_bfloat16*>(out), out_stride, static_cast<const __nv_bfloat16*>(x), stride, columns, act);
-    return b200_check_launch();
+    return launch_rc;
   }
   const dim3 grid(tokens, (columns + 255) / 256);
   if (dtype == B200_F32)
-    activate_columns_kernel<float><<<grid, 256, 0, stream>>>(static_cast<float*>(out), out_stride,
+    launch_rc = b200_launch(activate_columns_kernel<float>, dim3(grid), dim3(256), 0, stream, 0, static_cast<float*>(out), out_stride,
                                                              static_cast<const float*>(x), stride, columns, act);
   else if (dtype == B200_BF16)
-    activate_columns_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+    launch_rc = b200_launch(activate_columns_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, 0, 
         static_cast<__nv_bfloat16*>(out), out_stride, static_cast<const __nv_bfloat16*>(x), stride, columns, act);
   else
     return B200_BAD_DTYPE;
-  return b200_check_launch();
+  return launch_rc;
 }
 
 B200_EXPORT int b200_row_norm_gate(void* out, const float* o, const float* w, const void* g, int g_stride, int tokens,
@@ -330,6 +335,8 @@ __device__ __forceinline__ float glu_join(float g, float u, int kind, float limi
 template <typename T>
 __global__ void __launch_bounds__(256)
 glu_columns_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int ff, int kind, float limit, float alpha) {
+  pdl_launch_dependents();                          // the kernel after this one may be scheduled; it waits before it reads
+  pdl_wait();                                        // what this kernel reads belongs to the kernels before it
   const size_t t = blockIdx.x;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= ff) return;
@@ -342,6 +349,8 @@ glu_columns_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int ff, i
 template <typename T>
 __global__ void __launch_bounds__(256)
 glu_columns_vec_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int ff, int kind, float limit, float alpha) {
+  pdl_launch_dependents();                          // the kernel after this one may be scheduled; it waits before it reads
+  pdl_wait();                                        // what this kernel reads belongs to the kernels before it
   const size_t t = blockIdx.x;
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   if (c >= ff) return;
@@ -368,6 +377,8 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 act_table_mul_kernel(T* __restrict__ out, const T* __restrict__ z, const T* __restrict__ table, const int* __restrict__ ids,
                      int vocab, int table_width, int column, int dim, int act, int* err) {
+  pdl_launch_dependents();                          // the kernel after this one may be scheduled; it waits before it reads
+  pdl_wait();                                        // what this kernel reads belongs to the kernels before it
   const size_t t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) {
@@ -381,49 +392,51 @@ act_table_mul_kernel(T* __restrict__ out, const T* __restrict__ z, const T* __re
 
 B200_EXPORT int b200_glu_columns(void* out, const void* gate_up, int tokens, int ff, int kind, float limit, float alpha,
                                  int dtype, cudaStream_t stream) {
+  int launch_rc = 0;
   if (tokens <= 0 || ff <= 0) return 0;
   if (kind < 0 || kind > 1) return B200_BAD_SIZE;
   if (ff % 8 == 0) {
     const dim3 wide(tokens, (ff / 8 + 255) / 256);
     if (dtype == B200_F32)
-      glu_columns_vec_kernel<float><<<wide, 256, 0, stream>>>(static_cast<float*>(out),
+      launch_rc = b200_launch(glu_columns_vec_kernel<float>, dim3(wide), dim3(256), 0, stream, 0, static_cast<float*>(out),
                                                               static_cast<const float*>(gate_up), ff, kind, limit, alpha);
     else if (dtype == B200_BF16)
-      glu_columns_vec_kernel<__nv_bfloat16><<<wide, 256, 0, stream>>>(
+      launch_rc = b200_launch(glu_columns_vec_kernel<__nv_bfloat16>, dim3(wide), dim3(256), 0, stream, 0, 
           static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(gate_up), ff, kind, limit, alpha);
     else
       return B200_BAD_DTYPE;
-    return b200_check_launch();
+    return launch_rc;
   }
   const dim3 grid(tokens, (ff + 255) / 256);
   if (dtype == B200_F32)
-    glu_columns_kernel<float><<<grid, 256, 0, stream>>>(static_cast<float*>(out), static_cast<const float*>(gate_up), ff,
+    launch_rc = b200_launch(glu_columns_kernel<float>, dim3(grid), dim3(256), 0, stream, 0, static_cast<float*>(out), static_cast<const float*>(gate_up), ff,
                                                         kind, limit, alpha);
   else if (dtype == B200_BF16)
-    glu_columns_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+    launch_rc = b200_launch(glu_columns_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, 0, 
         static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(gate_up), ff, kind, limit, alpha);
   else
     return B200_BAD_DTYPE;
-  return b200_check_launch();
+  return launch_rc;
 }
 
 B200_EXPORT int b200_act_table_mul(void* out, const void* z, const void* table, const int* ids, int tokens, int vocab,
                                    int table_width, int column, int dim, int act, int dtype, int* err,
                                    cudaStream_t stream) {
+  int launch_rc = 0;
   if (tokens <= 0 || dim <= 0) return 0;
   if (act < ACT_SILU || act > ACT_RELU_SQUARED || vocab <= 0 || column < 0 || column + dim > table_width)
     return B200_BAD_SIZE;
   if (dtype == B200_F32)
-    act_table_mul_kernel<float><<<tokens, 128, 0, stream>>>(static_cast<float*>(out), static_cast<const float*>(z),
+    launch_rc = b200_launch(act_table_mul_kernel<float>, dim3(tokens), dim3(128), 0, stream, 0, static_cast<float*>(out), static_cast<const float*>(z),
                                                             static_cast<const float*>(table), ids, vocab, table_width,
                                                             column, dim, act, err);
   else if (dtype == B200_BF16)
-    act_table_mul_kernel<__nv_bfloat16><<<tokens, 128, 0, stream>>>(
+    launch_rc = b200_launch(act_table_mul_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), 0, stream, 0, 
         static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(z), static_cast<const __nv_bfloat16*>(table),
         ids, vocab, table_width, column, dim, act, err);
   else
     return B200_BAD_DTYPE;
-  return b200_check_launch();
+  return launch_rc;
 }
 
 // The whole gated read of a second token table for a step of few tokens, one cluster of SIDE_CLUSTER blocks a token,
@@ -444,6 +457,8 @@ token_side_few_kernel(float* stream, const T* x, const T* __restrict__ gate, con
                       const int* __restrict__ ids, const T* __restrict__ proj, const float* __restrict__ norm_w,
                       float eps, T* __restrict__ cast_out, int vocab, int table_width, int column, int dim, int width,
                       int slice, int act, int* err) {
+  pdl_launch_dependents();                          // the kernel after this one may be scheduled; it waits before it reads
+  pdl_wait();                                        // what this kernel reads belongs to the kernels before it
   constexpr int NW = SIDE_THREADS / 32;
   __shared__ float warp_part[NW];
   __shared__ float part[SIDE_CLUSTER];
@@ -541,18 +556,6 @@ B200_EXPORT int b200_token_side_few(float* stream, const void* x, const void* ga
   const int slice = (width + SIDE_CLUSTER - 1) / SIDE_CLUSTER;
   const size_t smem = (static_cast<size_t>(dim) + slice) * sizeof(float);
   if (smem > 200 * 1024) return B200_BAD_SIZE;
-  cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(tokens * SIDE_CLUSTER);
-  config.blockDim = dim3(SIDE_THREADS);
-  config.dynamicSmemBytes = smem;
-  config.stream = stream_;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = SIDE_CLUSTER;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  config.attrs = attr;
-  config.numAttrs = 1;
 #define B200_SIDE(T)                                                                                               \
   do {                                                                                                             \
     if (smem > 48 * 1024) {                                                                                        \
@@ -560,11 +563,11 @@ B200_EXPORT int b200_token_side_few(float* stream, const void* x, const void* ga
                                            static_cast<int>(smem));                                                \
       if (e != cudaSuccess) return static_cast<int>(e);                                                            \
     }                                                                                                              \
-    cudaError_t e = cudaLaunchKernelEx(&config, token_side_few_kernel<T>, stream, static_cast<const T*>(x),        \
-                                       static_cast<const T*>(gate), static_cast<const T*>(table), ids,             \
-                                       static_cast<const T*>(proj), norm_w, eps, static_cast<T*>(cast_out), vocab, \
-                                       table_width, column, dim, width, slice, act, err);                          \
-    if (e != cudaSuccess) return static_cast<int>(e);                                                              \
+    const int rc = b200_launch(token_side_few_kernel<T>, dim3(tokens * SIDE_CLUSTER), dim3(SIDE_THREADS), smem,    \
+                               stream_, SIDE_CLUSTER, stream, static_cast<const T*>(x), static_cast<const T*>(gate), \
+                               static_cast<const T*>(table), ids, static_cast<const T*>(proj), norm_w, eps,        \
+                               static_cast<T*>(cast_out), vocab, table_width, column, dim, width, slice, act, err); \
+    if (rc != 0) return rc;                                                                                        \
   } while (0)
   if (dtype == B200_F32) B200_SIDE(float);
   else if (dtype == B200_BF16) B200_SIDE(__nv_bfloat16);

@@ -31,6 +31,8 @@ template <typename TY, typename TO>
 __global__ void __launch_bounds__(PN_MAX_THREADS)
 norm_add_kernel(float* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ bias,
                 const float* __restrict__ w, float eps, TO* __restrict__ cast_out, int width) {
+  pdl_launch_dependents();                          // the kernel after this one may be scheduled; it waits before it reads
+  pdl_wait();                                        // what this kernel reads belongs to the kernels before it
   __shared__ float scratch[33];
   extern __shared__ float row[];                     // width floats: y + bias
   const size_t t = blockIdx.x;
@@ -81,6 +83,8 @@ template <typename TO>
 __global__ void __launch_bounds__(PN_THREADS)
 norm_rows_kernel(TO* __restrict__ out, const float* __restrict__ x, const int* __restrict__ rows,
                  const float* __restrict__ w, float eps, int width) {
+  pdl_launch_dependents();                          // the kernel after this one may be scheduled; it waits before it reads
+  pdl_wait();                                        // what this kernel reads belongs to the kernels before it
   __shared__ float scratch[33];
   const size_t r_out = blockIdx.x;
   const size_t t = rows != nullptr ? static_cast<size_t>(rows[r_out]) : r_out;
@@ -107,8 +111,9 @@ B200_EXPORT int b200_norm_add(float* x, const void* y, int y_dtype, const float*
                                            static_cast<int>(smem));                                            \
       if (e != cudaSuccess) return static_cast<int>(e);                                                        \
     }                                                                                                          \
-    norm_add_kernel<TY, TO><<<tokens, threads, smem, stream>>>(x, static_cast<const TY*>(y), bias, w, eps,      \
-                                                               static_cast<TO*>(cast_out), width);             \
+    const int rc = b200_launch(norm_add_kernel<TY, TO>, dim3(tokens), dim3(threads), smem, stream, 0, x,         \
+                               static_cast<const TY*>(y), bias, w, eps, static_cast<TO*>(cast_out), width);     \
+    if (rc != 0) return rc;                                                                                    \
   } while (0)
   const bool to_bf16 = cast_out != nullptr && out_dtype == B200_BF16;
   if (cast_out != nullptr && out_dtype != B200_BF16 && out_dtype != B200_F32) return B200_BAD_DTYPE;
@@ -128,9 +133,11 @@ B200_EXPORT int b200_norm_rows(void* out, int out_dtype, const float* x, const i
   if (n <= 0) return 0;
   if (width <= 0) return B200_BAD_SIZE;
   if (out_dtype == B200_F32)
-    norm_rows_kernel<float><<<n, PN_THREADS, 0, stream>>>(static_cast<float*>(out), x, rows, w, eps, width);
+    return b200_launch(norm_rows_kernel<float>, dim3(n), dim3(PN_THREADS), 0, stream, 0, static_cast<float*>(out), x, rows, w,
+                       eps, width);
   else if (out_dtype == B200_BF16)
-    norm_rows_kernel<__nv_bfloat16><<<n, PN_THREADS, 0, stream>>>(static_cast<__nv_bfloat16*>(out), x, rows, w, eps, width);
+    return b200_launch(norm_rows_kernel<__nv_bfloat16>, dim3(n), dim3(PN_THREADS), 0, stream, 0,
+                       static_cast<__nv_bfloat16*>(out), x, rows, w, eps, width);
   else
     return B200_BAD_DTYPE;
   return b200_check_launch();
