@@ -1,2 +1,2 @@
 """Importing this package registers the architectures that ship with the engine."""
-from . import kefetar, mukenex, qwen3, torinex  # noqa: F401
+from . import kefetar, lufizen, mukenex, qwen3, torinex  # noqa: F401

@@ -5,10 +5,14 @@
 //     row holds q (nh * d), k (nkv * d), v (nkv * dv) from column 0.  Optional, in this order: a bias per column;
 //     a per-head RMS norm of q and of k (x / sqrt(mean(x^2) + eps) * w, one weight vector for all heads);
 //     a rotation of the first rot_dims coordinates of every q and k head.  q goes to q_out [tokens, nh * d], k and
-//     v to the paged cache at the token's slot.
+//     v to the paged cache at the token's slot.  `flags`: PREP_NORM_PLAIN: q and k are normed without a weight
+//     (x / sqrt(mean(x^2) + eps)); PREP_NORM_AFTER_ROTATION: the norm follows the rotation instead of preceding it;
+//     PREP_VALUES_ARE_KEYS: the row holds no v columns and a token's value is its key as projected (with its bias,
+//     before norm and rotation; dv = d).
 //
 // (2) latent_prepare: attention over a narrow latent.  The packed row holds per head [d plain | r rotated] query
-//     coordinates (nh * (d + r)), then the down projection [c_dim latent | r rotated key part].  The latent is
+//     coordinates (nh * (d + r)), and a second row (`down`, which may be a column range of the same matrix or of
+//     another one) the down projection [c_dim latent | r rotated key part].  The latent is
 //     RMS-normed (weight w_c) and, with the rotated key part behind it, is the ONE key of the token
 //     (c_dim + r wide, shared by all heads); the latent alone is its value (stored a second time only if a value cache
 //     is given: attention can read it out of the key rows).  The query against that key is
@@ -26,6 +30,7 @@
 
 constexpr int MAX_VEC = 1024;       // widest vector a warp takes
 constexpr int WARPS = 4;
+enum : int { PREP_NORM_PLAIN = 1, PREP_NORM_AFTER_ROTATION = 2, PREP_VALUES_ARE_KEYS = 4 };
 
 __device__ __forceinline__ void rotate_row(float* row, int rot_dims, float pos, const float* __restrict__ inv_freq,
                                            bool interleaved, int lane) {
@@ -60,11 +65,12 @@ heads_prepare_kernel(const T* __restrict__ x, int in_stride, const float* __rest
                      const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
                      const float* __restrict__ inv_freq, int rot_dims, int interleaved,
                      const int* __restrict__ positions, const int* __restrict__ slots, int tokens, int nh, int nkv,
-                     int d, int dv, int page_size, long long cache_slots, T* __restrict__ q_out,
+                     int d, int dv, int flags, int page_size, long long cache_slots, T* __restrict__ q_out,
                      T* __restrict__ k_cache, T* __restrict__ v_cache, int* err) {
   __shared__ float buf[WARPS][MAX_VEC];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int vectors = nh + 2 * nkv;
+  const bool v_is_k = (flags & PREP_VALUES_ARE_KEYS) != 0;
   const long long work = static_cast<long long>(blockIdx.x) * WARPS + warp;
   if (work >= static_cast<long long>(tokens) * vectors) return;
   const int t = static_cast<int>(work / vectors);
@@ -72,7 +78,7 @@ heads_prepare_kernel(const T* __restrict__ x, int in_stride, const float* __rest
   const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
   const int kvh = is_q ? 0 : (is_k ? h - nh : h - nh - nkv);
   const int width = (is_q || is_k) ? d : dv;
-  const int col = is_q ? h * d : (is_k ? nh * d + kvh * d : (nh + nkv) * d + kvh * dv);
+  const int col = is_q ? h * d : ((is_k || v_is_k) ? nh * d + kvh * d : (nh + nkv) * d + kvh * dv);
   T* dst;
   if (is_q) {
     dst = q_out + (static_cast<size_t>(t) * nh + h) * d;
@@ -91,22 +97,34 @@ heads_prepare_kernel(const T* __restrict__ x, int in_stride, const float* __rest
     ss = fmaf(v, v, ss);
   }
   const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
-  if (w != nullptr) {
+  const bool normed = (is_q || is_k) && (w != nullptr || (flags & PREP_NORM_PLAIN) != 0);
+  const bool rotated = (is_q || is_k) && inv_freq != nullptr && rot_dims > 0;
+  const bool norm_last = (flags & PREP_NORM_AFTER_ROTATION) != 0;
+  if (normed && !norm_last) {
     ss = warp_sum(ss);
     const float r = 1.0f / sqrtf(ss / static_cast<float>(width) + eps);
-    for (int i = lane; i < width; i += 32) row[i] = row[i] * r * w[i];
+    for (int i = lane; i < width; i += 32) row[i] = w != nullptr ? row[i] * r * w[i] : row[i] * r;
   }
   __syncwarp();
-  if ((is_q || is_k) && inv_freq != nullptr && rot_dims > 0) {
+  if (rotated) {
     rotate_row(row, rot_dims, static_cast<float>(positions[t]), inv_freq, interleaved != 0, lane);
     __syncwarp();
+  }
+  if (normed && norm_last) {
+    ss = 0.0f;                                       // of the rotated row: the same sum up to rounding, taken as written
+    for (int i = lane; i < width; i += 32) ss = fmaf(row[i], row[i], ss);
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / static_cast<float>(width) + eps);
+    for (int i = lane; i < width; i += 32) dst[i] = from_f32<T>(w != nullptr ? row[i] * r * w[i] : row[i] * r);
+    return;
   }
   for (int i = lane; i < width; i += 32) dst[i] = from_f32<T>(row[i]);
 }
 
 template <typename T>
 __global__ void __launch_bounds__(WARPS * 32)
-latent_prepare_kernel(const T* __restrict__ x, int in_stride, const T* __restrict__ q_lat,
+latent_prepare_kernel(const T* __restrict__ x, int in_stride, const T* __restrict__ down, int down_stride,
+                      const T* __restrict__ q_lat,
                       const float* __restrict__ w_c, float eps, const float* __restrict__ inv_freq, int rot_dims,
                       int interleaved, const int* __restrict__ positions, const int* __restrict__ slots, int tokens,
                       int nh, int d, int r, int c_dim, int page_size, long long cache_slots, T* __restrict__ q_out,
@@ -137,7 +155,7 @@ latent_prepare_kernel(const T* __restrict__ x, int in_stride, const T* __restric
   }
   // the down projection: the normed latent and the rotated key part that all heads share
   if (slots == nullptr) return;
-  const T* src = x + static_cast<size_t>(t) * in_stride + static_cast<size_t>(nh) * (d + r);
+  const T* src = down + static_cast<size_t>(t) * down_stride;
   float ss = 0.0f;
   for (int i = lane; i < c_dim + r; i += 32) {
     const float v = to_f32<T>(src[i]);
@@ -294,30 +312,32 @@ joint_heads_prepare_kernel(const T* __restrict__ x, int in_stride, const float* 
 B200_EXPORT int b200_heads_prepare(const void* x, int dtype, int in_stride, const float* bias, const float* q_w,
                                    const float* k_w, float eps, const float* inv_freq, int rot_dims, int interleaved,
                                    const int* positions, const int* slots, int tokens, int nh, int nkv, int d, int dv,
-                                   int page_size, long long cache_slots, void* q_out, void* k_cache, void* v_cache,
-                                   int* err, cudaStream_t stream) {
+                                   int flags, int page_size, long long cache_slots, void* q_out, void* k_cache,
+                                   void* v_cache, int* err, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (nh <= 0 || nkv <= 0 || d <= 0 || dv <= 0 || d > MAX_VEC || dv > MAX_VEC || rot_dims < 0 || rot_dims > d ||
-      (rot_dims & 1) || page_size <= 0)
+      (rot_dims & 1) || page_size <= 0 || ((flags & PREP_VALUES_ARE_KEYS) && dv != d))
     return B200_BAD_SIZE;
   const long long work = static_cast<long long>(tokens) * (nh + 2 * nkv);
   const unsigned blocks = static_cast<unsigned>((work + WARPS - 1) / WARPS);
   if (dtype == B200_F32)
     heads_prepare_kernel<float><<<blocks, WARPS * 32, 0, stream>>>(
         static_cast<const float*>(x), in_stride, bias, q_w, k_w, eps, inv_freq, rot_dims, interleaved, positions, slots,
-        tokens, nh, nkv, d, dv, page_size, cache_slots, static_cast<float*>(q_out), static_cast<float*>(k_cache),
+        tokens, nh, nkv, d, dv, flags, page_size, cache_slots, static_cast<float*>(q_out), static_cast<float*>(k_cache),
         static_cast<float*>(v_cache), err);
   else if (dtype == B200_BF16)
     heads_prepare_kernel<__nv_bfloat16><<<blocks, WARPS * 32, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(x), in_stride, bias, q_w, k_w, eps, inv_freq, rot_dims, interleaved,
-        positions, slots, tokens, nh, nkv, d, dv, page_size, cache_slots, static_cast<__nv_bfloat16*>(q_out),
+        positions, slots, tokens, nh, nkv, d, dv, flags, page_size, cache_slots, static_cast<__nv_bfloat16*>(q_out),
         static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), err);
   else
     return B200_BAD_DTYPE;
   return b200_check_launch();
 }
 
-B200_EXPORT int b200_latent_prepare(const void* x, int dtype, int in_stride, const void* q_lat, const float* w_c,
+// x: the query rows (row stride in_stride); down: the down projection's rows [c_dim | r] (row stride down_stride).
+B200_EXPORT int b200_latent_prepare(const void* x, int dtype, int in_stride, const void* down, int down_stride,
+                                    const void* q_lat, const float* w_c,
                                     float eps, const float* inv_freq, int rot_dims, int interleaved,
                                     const int* positions, const int* slots, int tokens, int nh, int d, int r, int c_dim,
                                     int page_size, long long cache_slots, void* q_out, void* k_cache, void* v_cache,
@@ -330,13 +350,14 @@ B200_EXPORT int b200_latent_prepare(const void* x, int dtype, int in_stride, con
   const unsigned blocks = static_cast<unsigned>((work + WARPS - 1) / WARPS);
   if (dtype == B200_F32)
     latent_prepare_kernel<float><<<blocks, WARPS * 32, 0, stream>>>(
-        static_cast<const float*>(x), in_stride, static_cast<const float*>(q_lat), w_c, eps, inv_freq, rot_dims,
+        static_cast<const float*>(x), in_stride, static_cast<const float*>(down), down_stride,
+        static_cast<const float*>(q_lat), w_c, eps, inv_freq, rot_dims,
         interleaved, positions, slots, tokens, nh, d, r, c_dim, page_size, cache_slots, static_cast<float*>(q_out),
         static_cast<float*>(k_cache), static_cast<float*>(v_cache), err);
   else if (dtype == B200_BF16)
     latent_prepare_kernel<__nv_bfloat16><<<blocks, WARPS * 32, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(x), in_stride, static_cast<const __nv_bfloat16*>(q_lat), w_c, eps, inv_freq,
-        rot_dims, interleaved, positions, slots, tokens, nh, d, r, c_dim, page_size, cache_slots,
+        static_cast<const __nv_bfloat16*>(x), in_stride, static_cast<const __nv_bfloat16*>(down), down_stride,
+        static_cast<const __nv_bfloat16*>(q_lat), w_c, eps, inv_freq, rot_dims, interleaved, positions, slots, tokens, nh, d, r, c_dim, page_size, cache_slots,
         static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache),
         err);
   else
@@ -376,4 +397,44 @@ B200_EXPORT int b200_joint_heads_prepare(const void* x, int dtype, int in_stride
   else return B200_BAD_DTYPE;
 #undef B200_JOINT
   return b200_check_launch();
+}
+
+
+// (4) columns_rms_norm: out[t][:] = x[t][0 .. width) / sqrt(mean(x^2) + eps) * w, the rows of x `in_stride` apart
+//     (a column range of a wider projection), out contiguous.  One warp a row; sums in float in an order fixed by the
+//     lane layout.
+template <typename T>
+__global__ void __launch_bounds__(WARPS * 32)
+columns_rms_norm_kernel(const T* __restrict__ x, int in_stride, const float* __restrict__ w, float eps, int tokens,
+                        int width, T* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * WARPS + warp;
+  if (t >= tokens) return;
+  const T* src = x + static_cast<size_t>(t) * in_stride;
+  float ss = 0.0f;
+  for (int i = lane; i < width; i += 32) {
+    const float v = to_f32<T>(src[i]);
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  const float r = 1.0f / sqrtf(ss / static_cast<float>(width) + eps);
+  T* dst = out + static_cast<size_t>(t) * width;
+  for (int i = lane; i < width; i += 32) dst[i] = from_f32<T>(to_f32<T>(src[i]) * r * w[i]);
+}
+
+B200_EXPORT int b200_columns_rms_norm(const void* x, int dtype, int in_stride, const float* w, float eps, int tokens,
+                                      int width, void* out, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (width <= 0 || in_stride < width) return B200_BAD_SIZE;
+  const unsigned blocks = (tokens + WARPS - 1) / WARPS;
+  if (dtype == B200_F32)
+    return b200_launch(columns_rms_norm_kernel<float>, dim3(blocks), dim3(WARPS * 32), 0, stream, 0,
+                       static_cast<const float*>(x), in_stride, w, eps, tokens, width, static_cast<float*>(out));
+  if (dtype == B200_BF16)
+    return b200_launch(columns_rms_norm_kernel<__nv_bfloat16>, dim3(blocks), dim3(WARPS * 32), 0, stream, 0,
+                       static_cast<const __nv_bfloat16*>(x), in_stride, w, eps, tokens, width,
+                       static_cast<__nv_bfloat16*>(out));
+  return B200_BAD_DTYPE;
 }

@@ -12,7 +12,7 @@
 // ------------------------------------------------------------------ embedding
 template <typename TA, typename TW>
 __global__ void embedding_kernel(TA* __restrict__ out, const TW* __restrict__ table,
-                                 const int* __restrict__ ids, int width, int vocab, int* err) {
+                                 const int* __restrict__ ids, int width, int vocab, float scale, int* err) {
   const int row = blockIdx.x;
   const int id = ids[row];
   const bool ok = id >= 0 && id < vocab;
@@ -20,7 +20,7 @@ __global__ void embedding_kernel(TA* __restrict__ out, const TW* __restrict__ ta
   const TW* src = table + static_cast<size_t>(ok ? id : 0) * width;
   TA* dst = out + static_cast<size_t>(row) * width;
   for (int i = threadIdx.x; i < width; i += blockDim.x)
-    dst[i] = ok ? from_f32<TA>(to_f32<TW>(src[i])) : from_f32<TA>(0.0f);
+    dst[i] = ok ? from_f32<TA>(to_f32<TW>(src[i]) * scale) : from_f32<TA>(0.0f);      // scale 1: the row as stored
 }
 
 // ------------------------------------------------------------------ norms
@@ -170,11 +170,11 @@ __global__ void cast_kernel(TO* __restrict__ out, const TI* __restrict__ in, siz
   else return B200_BAD_DTYPE;
 
 B200_EXPORT int b200_embedding(void* out, const void* table, const int* ids, int tokens, int width,
-                               int vocab, int act_dtype, int table_dtype, int* err, cudaStream_t stream) {
+                               int vocab, float scale, int act_dtype, int table_dtype, int* err, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (width <= 0 || vocab <= 0) return B200_BAD_SIZE;
 #define CALL(TA, TW) embedding_kernel<TA, TW><<<tokens, 256, 0, stream>>>( \
-    static_cast<TA*>(out), static_cast<const TW*>(table), ids, width, vocab, err)
+    static_cast<TA*>(out), static_cast<const TW*>(table), ids, width, vocab, scale, err)
   DISPATCH2(act_dtype, table_dtype, CALL)
 #undef CALL
   return b200_check_launch();
@@ -265,4 +265,21 @@ B200_EXPORT int b200_cast(void* out, const void* in, long long total, int out_dt
   DISPATCH2(out_dtype, in_dtype, CALL)
 #undef CALL
   return b200_check_launch();
+}
+
+
+// ------------------------------------------------------------------ a constant factor
+// z <- z * scale in place on floats (a model whose logits carry a fixed factor).
+__global__ void __launch_bounds__(256) scale_floats_kernel(float* __restrict__ z, long long n, float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    z[i] *= scale;
+}
+
+B200_EXPORT int b200_scale_floats(float* z, long long n, float scale, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const unsigned blocks = static_cast<unsigned>(n + 255 < 256ll * 4096 ? (n + 255) / 256 : 4096);
+  return b200_launch(scale_floats_kernel, dim3(blocks), dim3(256), 0, stream, 0, z, n, scale);
 }

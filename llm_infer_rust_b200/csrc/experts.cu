@@ -339,17 +339,19 @@ expert_rows_few_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int* 
 }
 
 // ------------------------------------------------------------------ the experts' outputs back to the tokens
-// weight: one per pair, or null for `uniform` each.  add [tokens, width] (TA; a shared expert's output) joins the sum.
+// weight: one per pair, or null for `uniform` each.  add [tokens, width] (TA; a shared expert's output) joins the sum,
+// times add_scale[t] if that is given (a gate of the shared expert, one float a token).
 // grid (tokens, column tiles of 1,024): a thread takes four neighbouring columns (one where the width is no multiple
 // of four); the sum over k runs in order either way.
 template <typename TA>
 __global__ void __launch_bounds__(256)
 expert_combine_kernel(float* __restrict__ out, const float* __restrict__ Y, const int* __restrict__ pos_of_pair,
                       int top, int width, float uniform, const float* __restrict__ weight,
-                      const TA* __restrict__ add) {
+                      const TA* __restrict__ add, const float* __restrict__ add_scale) {
   pdl_launch_dependents();                          // the kernel after this one may be scheduled; it waits before it reads
   pdl_wait();                                        // what this kernel reads belongs to the kernels before it
   const size_t t = blockIdx.x;
+  const float as = (add != nullptr && add_scale != nullptr) ? add_scale[t] : 1.0f;
   if (width % 4 == 0) {
     const int c = (blockIdx.y * 256 + threadIdx.x) * 4;
     if (c >= width) return;
@@ -367,7 +369,7 @@ expert_combine_kernel(float* __restrict__ out, const float* __restrict__ Y, cons
     if (add != nullptr) {
       float a[4];
       load_floats<TA, 4>(add + t * width + c, a);
-      s[0] += a[0]; s[1] += a[1]; s[2] += a[2]; s[3] += a[3];
+      s[0] = fmaf(as, a[0], s[0]); s[1] = fmaf(as, a[1], s[1]); s[2] = fmaf(as, a[2], s[2]); s[3] = fmaf(as, a[3], s[3]);
     }
     *reinterpret_cast<float4*>(out + t * width + c) = make_float4(s[0], s[1], s[2], s[3]);
     return;
@@ -381,44 +383,55 @@ expert_combine_kernel(float* __restrict__ out, const float* __restrict__ Y, cons
       for (int k = 0; k < top; ++k)
         s = fmaf(weight[t * top + k], Y[static_cast<size_t>(pos_of_pair[t * top + k]) * width + c], s);
     }
-    if (add != nullptr) s += to_f32<TA>(add[t * width + c]);
+    if (add != nullptr) s = fmaf(as, to_f32<TA>(add[t * width + c]), s);
     out[t * width + c] = s;
   }
 }
 
 // ------------------------------------------------------------------ the router
-// z[t][e] = W[e] . x[t] in float (FFMA, whatever the dtype of x and W), scores = softmax over all experts (or a
-// sigmoid of each), experts in `groups` equal groups of neighbours, a group's score its largest score, only experts
-// of the `keep` best groups can be chosen, the `top` largest of them are, each weighted by its score (divided by
-// the chosen scores' sum if `renormalize`).  Ties go to the lower index.
+// z[t][e] = W[e] . x[t] in float (FFMA, whatever the dtype of x and W), scores s = softmax over all experts (or a
+// sigmoid of each).  The CHOICE looks at c = s + correction (one float an expert; null: c = s): experts in `groups`
+// equal groups of neighbours, a group's score the sum of its `group_members` largest c (1: its largest), only experts
+// of the `keep` best groups can be chosen (the others are shut out whatever their c, which may be negative), the `top`
+// largest c of them are.  The WEIGHTS are the chosen experts' s (without the correction), divided by their sum if
+// `renormalize`, times `gain_scale`.  Ties go to the lower index.
+// An extra row `gate_w` (null: none) gives gate_out[t] = sigmoid(gate_w . x[t]), summed like a logit: the gate of
+// something that every token takes besides its experts.
 // A block takes TT tokens (1 for a step of few tokens, so that they spread over the SMs; 4 otherwise): warp w
-// multiplies experts 2w, 2w + 1, then 2w + 16, .. for all of them (a row of W is read once a block), then warp t
+// multiplies rows 2w, 2w + 1, then 2w + 16, .. for all of them (a row of W is read once a block), then warp t
 // chooses for token t.  A logit is summed the same way whatever the block holds: lane l takes columns
 // 8 l .. 8 l + 7, then 256 further on and so on, in order, and the lanes' sums meet in a butterfly.  Rows that start
-// on 16 bytes are read in 16-byte pieces.  Shared memory: TT * experts floats (logits, then scores) and as many ints.
+// on 16 bytes are read in 16-byte pieces.  Shared memory a token: experts + 1 floats (logits, then scores), experts
+// floats (what the choice looks at) and experts ints.
 constexpr int ROUTER_WARPS = 8;
 
 template <typename TX, typename TW, int TT>
 __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 expert_router_kernel(const TX* __restrict__ x, const TW* __restrict__ W, int tokens, int width, int experts,
-                     int groups, int keep, int top, int sigmoid_scores, int renormalize, int* __restrict__ choice,
+                     int groups, int keep, int top, int sigmoid_scores, int renormalize,
+                     const float* __restrict__ correction, int group_members, float gain_scale,
+                     const TW* __restrict__ gate_w, float* __restrict__ gate_out, int* __restrict__ choice,
                      float* __restrict__ weight) {
   pdl_launch_dependents();                          // the kernel after this one may be scheduled; it waits before it reads
   pdl_wait();                                        // what this kernel reads belongs to the kernels before it
   extern __shared__ float rsm[];
-  float* z = rsm;                                                   // [TT][experts]
-  int* open = reinterpret_cast<int*>(rsm + TT * experts);           // [TT][experts]: may still be chosen
+  const int zs = experts + 1;                                       // a token's logits, then the extra row's
+  float* z = rsm;                                                   // [TT][experts + 1]
+  float* look = rsm + TT * zs;                                      // [TT][experts]: what the choice compares
+  int* open = reinterpret_cast<int*>(look + TT * experts);          // [TT][experts]: may still be chosen
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t0 = blockIdx.x * TT;
   const int nt = min(TT, tokens - t0);
-  const bool wide = width % 8 == 0;                                 // every row of x and W starts on 16 bytes
-  for (int e0 = 2 * warp; e0 < experts; e0 += 2 * ROUTER_WARPS) {
-    const bool two = e0 + 1 < experts;
+  const bool wide = width % 8 == 0 && (gate_w == nullptr || reinterpret_cast<uintptr_t>(gate_w) % 16 == 0);
+  const int rows = experts + (gate_w != nullptr ? 1 : 0);
+  for (int e0 = 2 * warp; e0 < rows; e0 += 2 * ROUTER_WARPS) {
+    const bool two = e0 + 1 < rows;
     float acc[2][TT];
 #pragma unroll
     for (int i = 0; i < TT; ++i) acc[0][i] = acc[1][i] = 0.0f;
-    const TW* w0 = W + static_cast<size_t>(e0) * width;
-    const TW* w1 = W + static_cast<size_t>(two ? e0 + 1 : e0) * width;
+    const int e1 = two ? e0 + 1 : e0;
+    const TW* w0 = e0 < experts ? W + static_cast<size_t>(e0) * width : gate_w;
+    const TW* w1 = e1 < experts ? W + static_cast<size_t>(e1) * width : gate_w;
     const TX* xs = x + static_cast<size_t>(t0) * width;
     if (wide) {
 #pragma unroll 2
@@ -456,16 +469,18 @@ expert_router_kernel(const TX* __restrict__ x, const TW* __restrict__ W, int tok
     for (int i = 0; i < TT; ++i) {
       const float v0 = warp_sum(acc[0][i]), v1 = warp_sum(acc[1][i]);
       if (lane == 0 && i < nt) {
-        z[i * experts + e0] = v0;
-        if (two) z[i * experts + e0 + 1] = v1;
+        z[i * zs + e0] = v0;
+        if (two) z[i * zs + e0 + 1] = v1;
       }
     }
   }
   __syncthreads();
   if (warp >= nt) return;
-  float* s = z + warp * experts;
+  float* s = z + warp * zs;
+  float* c = look + warp * experts;
   int* can = open + warp * experts;
   const int t = t0 + warp;
+  if (gate_w != nullptr && lane == 0) gate_out[t] = 1.0f / (1.0f + expf(-s[experts]));
   if (sigmoid_scores) {
     for (int e = lane; e < experts; e += 32) s[e] = 1.0f / (1.0f + expf(-s[e]));
   } else {
@@ -477,7 +492,10 @@ expert_router_kernel(const TX* __restrict__ x, const TW* __restrict__ W, int tok
     sum = warp_sum(sum);
     for (int e = lane; e < experts; e += 32) s[e] = s[e] / sum;
   }
-  for (int e = lane; e < experts; e += 32) can[e] = groups <= 1 ? 1 : 0;
+  for (int e = lane; e < experts; e += 32) {
+    can[e] = groups <= 1 ? 1 : 0;
+    c[e] = correction != nullptr ? s[e] + correction[e] : s[e];
+  }
   __syncwarp();
   const int per = experts / max(groups, 1);
   // argmax over lanes of (value, lower index first)
@@ -492,13 +510,35 @@ expert_router_kernel(const TX* __restrict__ x, const TW* __restrict__ W, int tok
   };
   if (groups > 1) {
     // the keep best groups, one at a time; `can` of a group's first expert doubles as "group taken"
+    const int members = min(max(group_members, 1), per);
     for (int r = 0; r < keep; ++r) {
       float bv = -INFINITY;
       int bi = 0x7fffffff;
       for (int g = lane; g < groups; g += 32) {
         if (can[g * per] != 0) continue;
-        float gm = -INFINITY;
-        for (int j = 0; j < per; ++j) gm = fmaxf(gm, s[g * per + j]);
+        const float* cg = c + g * per;
+        float gm;
+        if (members == 1) {
+          gm = -INFINITY;
+          for (int j = 0; j < per; ++j) gm = fmaxf(gm, cg[j]);
+        } else {
+          // the sum of the group's `members` largest, taken in the order (larger first, lower index first)
+          gm = 0.0f;
+          float pv = INFINITY;
+          int pj = -1;
+          for (int n = 0; n < members; ++n) {
+            float mv = -INFINITY;
+            int mj = per;
+            for (int j = 0; j < per; ++j) {
+              const float v = cg[j];
+              const bool after = v < pv || (v == pv && j > pj);          // not yet taken
+              if (after && (v > mv || (v == mv && j < mj))) { mv = v; mj = j; }
+            }
+            if (mj == per) break;
+            gm += mv;
+            pv = mv; pj = mj;
+          }
+        }
         if (gm > bv || (gm == bv && g < bi)) { bv = gm; bi = g; }
       }
       const int g = best_of(bv, bi);
@@ -513,7 +553,7 @@ expert_router_kernel(const TX* __restrict__ x, const TW* __restrict__ W, int tok
     float bv = -INFINITY;
     int bi = 0x7fffffff;
     for (int e = lane; e < experts; e += 32)
-      if (can[e] == 1 && (s[e] > bv || (s[e] == bv && e < bi))) { bv = s[e]; bi = e; }
+      if (can[e] == 1 && (c[e] > bv || (c[e] == bv && e < bi))) { bv = c[e]; bi = e; }
     const int e = best_of(bv, bi);
     __syncwarp();
     if (lane == 0) {
@@ -524,8 +564,11 @@ expert_router_kernel(const TX* __restrict__ x, const TW* __restrict__ W, int tok
     if (e != 0x7fffffff) total += s[e];
     __syncwarp();
   }
-  if (renormalize && lane == 0 && total > 0.0f)
-    for (int r = 0; r < top; ++r) weight[static_cast<size_t>(t) * top + r] /= total;
+  if (lane == 0) {
+    const float f = (renormalize && total > 0.0f) ? gain_scale / total : gain_scale;
+    if (f != 1.0f)
+      for (int r = 0; r < top; ++r) weight[static_cast<size_t>(t) * top + r] *= f;
+  }
 }
 
 // ------------------------------------------------------------------ C interface
@@ -562,6 +605,7 @@ struct ExpertChoice {
   const float* weight;
   const void* add;
   int add_dtype;
+  const float* add_scale;      // null, or one factor a token for `add`
 };
 
 static int launch_combine(float* out, const float* y, const int* pos_of_pair, int tokens, int top, int width,
@@ -570,9 +614,9 @@ static int launch_combine(float* out, const float* y, const int* pos_of_pair, in
   const dim3 combine_grid(tokens, (width + 1023) / 1024);
   if (c.add != nullptr && c.add_dtype == B200_BF16)
     return b200_launch(expert_combine_kernel<__nv_bfloat16>, combine_grid, dim3(256), 0, stream, 0, out, y, pos_of_pair,
-                       top, width, uniform, c.weight, static_cast<const __nv_bfloat16*>(c.add));
+                       top, width, uniform, c.weight, static_cast<const __nv_bfloat16*>(c.add), c.add_scale);
   return b200_launch(expert_combine_kernel<float>, combine_grid, dim3(256), 0, stream, 0, out, y, pos_of_pair, top, width,
-                     uniform, c.weight, static_cast<const float*>(c.add));
+                     uniform, c.weight, static_cast<const float*>(c.add), c.add_scale);
 }
 
 // x [tokens, width] -> out [tokens, width] float32.  `h` holds pairs * ff elements of x's dtype, `y` pairs * width
@@ -631,29 +675,32 @@ static int run_experts(const void* x, int dtype, const ExpertChoice& c, int top,
 B200_EXPORT int b200_table_experts(const void* x, int dtype, const int* token_ids, const int* table, int vocab, int top,
                                    int experts, const void* gate_up, const void* down, int tokens, int width, int ff,
                                    void* h, float* y, int* route, float* out, int* err, cudaStream_t stream) {
-  const ExpertChoice c = {token_ids, table, vocab, nullptr, nullptr, nullptr, B200_F32};
+  const ExpertChoice c = {token_ids, table, vocab, nullptr, nullptr, nullptr, B200_F32, nullptr};
   return run_experts(x, dtype, c, top, experts, gate_up, down, tokens, width, ff, GluAct{0, 0.0f, 0.0f}, h, y, route,
                      out, err, stream);
 }
 
 // The router alone: choice [tokens, top] ints and weight [tokens, top] floats.  x_dtype / w_dtype: B200_F32 or
-// B200_BF16 each; the products are FFMA either way.
+// B200_BF16 each; the products are FFMA either way.  correction (null or [experts] floats), group_members, gain_scale,
+// gate_w (null or one more row of w's dtype) and gate_out ([tokens] floats): see the kernel.
 B200_EXPORT int b200_expert_router(const void* x, int x_dtype, const void* w, int w_dtype, int tokens, int width,
                                    int experts, int groups, int keep, int top, int sigmoid_scores, int renormalize,
-                                   int* choice, float* weight, cudaStream_t stream) {
+                                   const float* correction, int group_members, float gain_scale, const void* gate_w,
+                                   float* gate_out, int* choice, float* weight, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (width <= 0 || experts <= 0 || groups <= 0 || experts % groups || keep <= 0 || keep > groups || top <= 0 ||
-      top > keep * (experts / groups))
+      top > keep * (experts / groups) || group_members <= 0 || (gate_w != nullptr && gate_out == nullptr))
     return B200_BAD_SIZE;
   const int per_block = tokens <= 148 ? 1 : 4;
-  const size_t smem = static_cast<size_t>(per_block) * experts * (sizeof(float) + sizeof(int));
-  if (static_cast<size_t>(8) * experts * (sizeof(float) + sizeof(int)) > 48 * 1024) return B200_BAD_SIZE;
+  const size_t per_token = (static_cast<size_t>(experts) + 1) * sizeof(float) + experts * (sizeof(float) + sizeof(int));
+  const size_t smem = per_block * per_token;
+  if (8 * per_token > 48 * 1024) return B200_BAD_SIZE;
   const unsigned blocks = (tokens + per_block - 1) / per_block;
   int router_rc = 0;
 #define B200_ROUTER_TT(TX, TW, TT)                                                                                   \
   router_rc = b200_launch(expert_router_kernel<TX, TW, TT>, dim3(blocks), dim3(ROUTER_WARPS * 32), smem, stream, 0,  \
       static_cast<const TX*>(x), static_cast<const TW*>(w), tokens, width, experts, groups, keep, top, sigmoid_scores, \
-      renormalize, choice, weight)
+      renormalize, correction, group_members, gain_scale, static_cast<const TW*>(gate_w), gate_out, choice, weight)
 #define B200_ROUTER(TX, TW)                                                                                          \
   do {                                                                                                               \
     if (per_block == 1) B200_ROUTER_TT(TX, TW, 1);                                                                   \
@@ -670,13 +717,15 @@ B200_EXPORT int b200_expert_router(const void* x, int x_dtype, const void* w, in
 }
 
 // Experts chosen by a router: choice and weight [tokens, top] (b200_expert_router), glu kind `act_kind` with `limit`
-// and `alpha`, `add` (null, or [tokens, width] of add_dtype: what every token gets besides, e.g. a shared expert).
+// and `alpha`, `add` (null, or [tokens, width] of add_dtype: what every token gets besides, e.g. a shared expert),
+// `add_scale` (null, or one float a token that multiplies its row of `add`).
 B200_EXPORT int b200_routed_experts(const void* x, int dtype, const int* choice, const float* weight, int top,
                                     int experts, const void* gate_up, const void* down, int tokens, int width, int ff,
-                                    int act_kind, float limit, float alpha, const void* add, int add_dtype, void* h,
-                                    float* y, int* route, float* out, int* err, cudaStream_t stream) {
+                                    int act_kind, float limit, float alpha, const void* add, int add_dtype,
+                                    const float* add_scale, void* h, float* y, int* route, float* out, int* err,
+                                    cudaStream_t stream) {
   if (choice == nullptr || weight == nullptr || act_kind < 0 || act_kind > 1) return B200_BAD_SIZE;
-  const ExpertChoice c = {nullptr, nullptr, 0, choice, weight, add, add_dtype};
+  const ExpertChoice c = {nullptr, nullptr, 0, choice, weight, add, add_dtype, add_scale};
   return run_experts(x, dtype, c, top, experts, gate_up, down, tokens, width, ff, GluAct{act_kind, limit, alpha}, h, y,
                      route, out, err, stream);
 }

@@ -219,7 +219,7 @@ B200_EXPORT int b200_table_experts_tcgen05(const void* x, const int* token_ids, 
                                            int experts, const void* gate_up, const void* down, int tokens, int width,
                                            int ff, void* xs, void* h, float* y, int* route, float* out, int* err,
                                            cudaStream_t stream) {
-  const ExpertChoice c = {token_ids, table, vocab, nullptr, nullptr, nullptr, B200_F32};
+  const ExpertChoice c = {token_ids, table, vocab, nullptr, nullptr, nullptr, B200_F32, nullptr};
   return run_experts_tcgen05(x, c, top, experts, gate_up, down, tokens, width, ff, GluAct{0, 0.0f, 0.0f}, xs, h, y,
                              route, out, err, stream);
 }
@@ -228,10 +228,10 @@ B200_EXPORT int b200_table_experts_tcgen05(const void* x, const int* token_ids, 
 B200_EXPORT int b200_routed_experts_tcgen05(const void* x, const int* choice, const float* weight, int top, int experts,
                                             const void* gate_up, const void* down, int tokens, int width, int ff,
                                             int act_kind, float limit, float alpha, const void* add, int add_dtype,
-                                            void* xs, void* h, float* y, int* route, float* out, int* err,
+                                            const float* add_scale, void* xs, void* h, float* y, int* route, float* out, int* err,
                                             cudaStream_t stream) {
   if (choice == nullptr || weight == nullptr || act_kind < 0 || act_kind > 1) return B200_BAD_SIZE;
-  const ExpertChoice c = {nullptr, nullptr, 0, choice, weight, add, add_dtype};
+  const ExpertChoice c = {nullptr, nullptr, 0, choice, weight, add, add_dtype, add_scale};
   return run_experts_tcgen05(x, c, top, experts, gate_up, down, tokens, width, ff, GluAct{act_kind, limit, alpha}, xs,
                              h, y, route, out, err, stream);
 }

@@ -3,7 +3,7 @@
 //   poly_norm            out = a N(z) + b N(z^2) + c N(z^3) + e,  N(y) = y / sqrt(mean(y^2) + eps) over a token's
 //                        vector, powers taken element by element; (a, b, c, e) are four floats on the device
 //   head_unit_norm_gate  out[t][h][:] = o[t][h][:] / sqrt(mean(o[t][h][:]^2) + eps) * silu(g[t][h][:])
-//   sigmoid_gate_mul     out[t][c] = a[t][c] * sigmoid(g[t][c])
+//   sigmoid_gate_mul     out[t][c] = a[t][c] * sigmoid(g[t][c / per])   (per 1: a gate a column; a head's size: a gate a head)
 //   activate_columns     x[t][c] <- act(x[t][c]) for the first `columns` columns of rows `stride` wide (in place), or
 //                        out[t][c] = act(x[t][c]); act: 1 silu, 2 gelu with erf, 3 gelu with tanh
 //   row_norm_gate        out[t][:] = o[t][:] / sqrt(mean(o[t][:]^2) + eps) * w[:] * sigmoid(g[t][:])   (o in float)
@@ -134,10 +134,10 @@ head_unit_norm_gate_kernel(T* __restrict__ out, const float* __restrict__ o, con
 
 template <typename T>
 __global__ void __launch_bounds__(256)
-sigmoid_gate_mul_kernel(T* out, const T* a, const T* __restrict__ g, int g_stride, int width) {   // out may be a
+sigmoid_gate_mul_kernel(T* out, const T* a, const T* __restrict__ g, int g_stride, int width, int per) {   // out may be a
   const size_t t = blockIdx.x;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
-    const float x = to_f32<T>(g[t * g_stride + c]);
+    const float x = to_f32<T>(g[t * g_stride + (per == 1 ? c : c / per)]);
     out[t * width + c] = from_f32<T>(to_f32<T>(a[t * width + c]) / (1.0f + expf(-x)));
   }
 }
@@ -186,16 +186,16 @@ B200_EXPORT int b200_head_unit_norm_gate(void* out, const float* o, const void* 
 }
 
 B200_EXPORT int b200_sigmoid_gate_mul(void* out, const void* a, const void* g, int g_stride, int tokens, int width,
-                                      int dtype, cudaStream_t stream) {
+                                      int per, int dtype, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (width <= 0) return B200_BAD_SIZE;
+  if (width <= 0 || per <= 0 || width % per) return B200_BAD_SIZE;
   if (dtype == B200_F32)
     sigmoid_gate_mul_kernel<float><<<tokens, 256, 0, stream>>>(static_cast<float*>(out), static_cast<const float*>(a),
-                                                               static_cast<const float*>(g), g_stride, width);
+                                                               static_cast<const float*>(g), g_stride, width, per);
   else if (dtype == B200_BF16)
     sigmoid_gate_mul_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(
         static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(g),
-        g_stride, width);
+        g_stride, width, per);
   else
     return B200_BAD_DTYPE;
   return b200_check_launch();

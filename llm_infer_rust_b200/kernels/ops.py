@@ -172,14 +172,15 @@ def _attention(head_dim: int):
 
 
 # --------------------------------------------------------------------------- element-wise
-def embedding(ids: torch.Tensor, table: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+def embedding(ids: torch.Tensor, table: torch.Tensor, out_dtype: torch.dtype, scale: float = 1.0) -> torch.Tensor:
+    """out[t] = table[ids[t]] * scale (the product in float, rounded once to ``out_dtype``)."""
     _cuda(ids, table)
     _contig(ids, table)
     if ids.dtype != torch.int32:
         raise KernelError("token ids must be int32")
     out = torch.empty((ids.numel(), table.shape[1]), dtype=out_dtype, device=table.device)
     rc = _elementwise().b200_embedding(_p(out), _p(table), _p(ids), ids.numel(), table.shape[1],
-                                       table.shape[0], _code(out), _code(table),
+                                       table.shape[0], ctypes.c_float(scale), _code(out), _code(table),
                                        _p(error_word(table.device)), _stream())
     _ok(rc, "embedding")
     return out
@@ -243,6 +244,16 @@ def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     rc = _elementwise().b200_cast(_p(out), _p(x), ctypes.c_longlong(x.numel()), _code(out), _code(x), _stream())
     _ok(rc, "cast")
     return out
+
+
+def scale_floats(z: torch.Tensor, scale: float) -> torch.Tensor:
+    """z <- z * scale in place on a contiguous float32 tensor."""
+    _cuda(z)
+    _contig(z)
+    _f32(z)
+    rc = _elementwise().b200_scale_floats(_p(z), ctypes.c_longlong(z.numel()), ctypes.c_float(scale), _stream())
+    _ok(rc, "scale_floats")
+    return z
 
 
 # --------------------------------------------------------------------------- between QKV and attention
@@ -1568,15 +1579,16 @@ def head_unit_norm_gate(o: torch.Tensor, packed: torch.Tensor, gate_column: int,
     return out
 
 
-def sigmoid_gate_mul(a: torch.Tensor, packed: torch.Tensor, gate_column: int) -> torch.Tensor:
-    """a * sigmoid(gate), the gate lying in ``packed`` from column ``gate_column`` on; in place."""
+def sigmoid_gate_mul(a: torch.Tensor, packed: torch.Tensor, gate_column: int, per: int = 1) -> torch.Tensor:
+    """a * sigmoid(gate), the gate lying in ``packed`` from column ``gate_column`` on; in place.  ``per``: how many
+    neighbouring columns of ``a`` share one gate value (1: a gate a column; a head's size: one gate a head)."""
     _cuda(a, packed)
     _contig(a, packed)
-    if a.dtype != packed.dtype or packed.shape[1] < gate_column + a.shape[1]:
+    if per <= 0 or a.shape[1] % per or a.dtype != packed.dtype or packed.shape[1] < gate_column + a.shape[1] // per:
         raise KernelError("sigmoid_gate_mul: dtype or columns do not fit")
     gate = packed.view(-1)[gate_column:]
     rc = _gated().b200_sigmoid_gate_mul(_p(a), _p(a), ctypes.c_void_p(gate.data_ptr()), packed.shape[1], a.shape[0],
-                                        a.shape[1], _code(a), _stream())
+                                        a.shape[1], int(per), _code(a), _stream())
     _ok(rc, "sigmoid_gate_mul")
     return a
 
@@ -1668,15 +1680,21 @@ def heads_prepare(x: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor, v
                   positions: torch.Tensor, slots: Optional[torch.Tensor], num_heads: int, num_kv_heads: int,
                   head_dim: int, v_head_dim: int, bias: Optional[torch.Tensor] = None,
                   q_weight: Optional[torch.Tensor] = None, k_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
-                  inv_freq: Optional[torch.Tensor] = None, rot_dims: int = 0, interleaved: bool = True) -> None:
+                  inv_freq: Optional[torch.Tensor] = None, rot_dims: int = 0, interleaved: bool = True,
+                  plain_norm: bool = False, norm_after_rotation: bool = False, values_are_keys: bool = False) -> None:
     """q, k, v are the first columns of ``x``: optional bias (float32, one per column), optional per-head RMS norm
-    of q and k (float32 weights over a head), optional rotation of the first ``rot_dims`` coordinates of every q
-    and k head by position * inv_freq (pairs (2i, 2i+1) if ``interleaved`` else (i, i + rot_dims/2)); q to ``q_out``,
-    k and v into the paged cache at ``slots`` (None: nothing is stored)."""
+    of q and k (float32 weights over a head; ``plain_norm``: no weights, x / sqrt(mean(x^2) + eps)), optional rotation
+    of the first ``rot_dims`` coordinates of every q and k head by position * inv_freq (pairs (2i, 2i+1) if
+    ``interleaved`` else (i, i + rot_dims/2)); the norm precedes the rotation unless ``norm_after_rotation``; q to
+    ``q_out``, k and v into the paged cache at ``slots`` (None: nothing is stored).  ``values_are_keys``: ``x`` holds
+    no v columns and a token's value is its key as projected (biased, neither normed nor rotated)."""
     _cuda(x, q_out, k_cache, v_cache, positions, slots, bias, q_weight, k_weight, inv_freq)
     _contig(x, q_out, k_cache, v_cache, positions, slots, bias, q_weight, k_weight, inv_freq)
     _f32(bias, q_weight, k_weight, inv_freq)
-    c = (num_heads + num_kv_heads) * head_dim + num_kv_heads * v_head_dim
+    if values_are_keys and v_head_dim != head_dim:
+        raise KernelError("values that are the keys are as wide as the keys")
+    c = (num_heads + num_kv_heads) * head_dim + (0 if values_are_keys else num_kv_heads * v_head_dim)
+    flags = (1 if plain_norm else 0) | (2 if norm_after_rotation else 0) | (4 if values_are_keys else 0)
     if x.shape[1] < c or q_out.dtype != x.dtype or k_cache.dtype != x.dtype or v_cache.dtype != x.dtype:
         raise KernelError("heads_prepare: the projection is too narrow, or q, cache and projection differ in dtype")
     if tuple(k_cache.shape[1:]) != (num_kv_heads, k_cache.shape[2], head_dim) or \
@@ -1691,8 +1709,9 @@ def heads_prepare(x: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor, v
     rc = load_cuda_library("attention_prepare.cu").b200_heads_prepare(
         _p(x), _code(x), x.shape[1], _p(bias), _p(q_weight), _p(k_weight), ctypes.c_float(eps), _p(inv_freq),
         int(rot_dims if inv_freq is not None else 0), int(bool(interleaved)), _p(positions), _p(slots), x.shape[0],
-        num_heads, num_kv_heads, head_dim, v_head_dim, page_size, ctypes.c_longlong(k_cache.shape[0] * page_size),
-        _p(q_out), _p(k_cache), _p(v_cache), _p(error_word(x.device)), _stream())
+        num_heads, num_kv_heads, head_dim, v_head_dim, flags, page_size,
+        ctypes.c_longlong(k_cache.shape[0] * page_size), _p(q_out), _p(k_cache), _p(v_cache),
+        _p(error_word(x.device)), _stream())
     _ok(rc, "heads_prepare")
 
 
@@ -1737,16 +1756,24 @@ def joint_heads_prepare(x: torch.Tensor, q_out: torch.Tensor, k_cache: Optional[
 def latent_prepare(x: torch.Tensor, q_lat: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor,
                    v_cache: Optional[torch.Tensor], latent_weight: torch.Tensor, eps: float, positions: torch.Tensor,
                    slots: Optional[torch.Tensor], num_heads: int, head_dim: int, rot_dim: int, latent_dim: int,
-                   inv_freq: Optional[torch.Tensor] = None, rot_dims: int = 0, interleaved: bool = True) -> None:
+                   inv_freq: Optional[torch.Tensor] = None, rot_dims: int = 0, interleaved: bool = True,
+                   down: Optional[torch.Tensor] = None) -> None:
     """``x`` holds per head [head_dim plain | rot_dim rotated] query coordinates, then [latent_dim | rot_dim] of the
-    down projection.  The latent is RMS-normed (``latent_weight``) and stored with the rotated key part behind it as
+    down projection; or ``down`` holds the latter (a view with a unit inner stride whose first latent_dim + rot_dim
+    columns are read: a column range of another matrix).  The latent is RMS-normed (``latent_weight``) and stored with the rotated key part behind it as
     the token's one key [latent_dim + rot_dim] and, if a value cache is given, alone as its value; the query that meets such keys is
     [q_lat[h, t] | rotated part] and goes to ``q_out`` [tokens, heads * (latent_dim + rot_dim)]."""
-    _cuda(x, q_lat, q_out, k_cache, v_cache, latent_weight, positions, slots, inv_freq)
+    _cuda(x, q_lat, q_out, k_cache, v_cache, latent_weight, positions, slots, inv_freq, down)
     _contig(x, q_lat, q_out, k_cache, v_cache, latent_weight, positions, slots, inv_freq)
     _f32(latent_weight, inv_freq)
     tokens = x.shape[0]
-    if x.shape[1] < num_heads * (head_dim + rot_dim) + latent_dim + rot_dim or \
+    q_columns = num_heads * (head_dim + rot_dim)
+    if down is None:
+        down = x[:, q_columns:]
+    if down.dim() != 2 or down.shape[0] != tokens or down.shape[1] < latent_dim + rot_dim or down.stride(1) != 1 or \
+            down.dtype != x.dtype:
+        raise KernelError("latent_prepare: the down projection's rows do not fit")
+    if x.shape[1] < q_columns or \
             tuple(q_lat.shape) != (num_heads, tokens, latent_dim) or latent_weight.numel() != latent_dim or \
             q_lat.dtype != x.dtype or q_out.dtype != x.dtype or k_cache.dtype != x.dtype or \
             (v_cache is not None and v_cache.dtype != x.dtype):
@@ -1758,11 +1785,26 @@ def latent_prepare(x: torch.Tensor, q_lat: torch.Tensor, q_out: torch.Tensor, k_
         raise KernelError("one frequency for every rotated pair is needed")
     page_size = k_cache.shape[2]
     rc = load_cuda_library("attention_prepare.cu").b200_latent_prepare(
-        _p(x), _code(x), x.shape[1], _p(q_lat), _p(latent_weight), ctypes.c_float(eps), _p(inv_freq),
+        _p(x), _code(x), x.shape[1], ctypes.c_void_p(down.data_ptr()), down.stride(0), _p(q_lat), _p(latent_weight), ctypes.c_float(eps), _p(inv_freq),
         int(rot_dims if inv_freq is not None else 0), int(bool(interleaved)), _p(positions), _p(slots), tokens,
         num_heads, head_dim, rot_dim, latent_dim, page_size, ctypes.c_longlong(k_cache.shape[0] * page_size),
         _p(q_out), _p(k_cache), _p(v_cache), _p(error_word(x.device)), _stream())
     _ok(rc, "latent_prepare")
+
+
+def columns_rms_norm(x: torch.Tensor, width: int, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMS norm (with ``weight``, float32) of the first ``width`` columns of every row of ``x`` [tokens, >= width]
+    (contiguous): a new contiguous [tokens, width] tensor of x's dtype."""
+    _cuda(x, weight)
+    _contig(x, weight)
+    _f32(weight)
+    if x.dim() != 2 or x.shape[1] < width or weight.numel() != width:
+        raise KernelError("columns_rms_norm: the rows are too narrow or the weight does not fit")
+    out = torch.empty((x.shape[0], width), dtype=x.dtype, device=x.device)
+    rc = load_cuda_library("attention_prepare.cu").b200_columns_rms_norm(
+        _p(x), _code(x), x.shape[1], _p(weight), ctypes.c_float(eps), x.shape[0], int(width), _p(out), _stream())
+    _ok(rc, "columns_rms_norm")
+    return out
 
 
 # --------------------------------------------------------------------------- experts chosen by a table or a router
@@ -1822,38 +1864,51 @@ def table_experts(x: torch.Tensor, token_ids: torch.Tensor, table: torch.Tensor,
 
 
 def expert_router(x: torch.Tensor, weight: torch.Tensor, top: int, groups: int = 1, keep: int = 1,
-                  scores: str = "softmax", renormalize: bool = False):
+                  scores: str = "softmax", renormalize: bool = False, correction: Optional[torch.Tensor] = None,
+                  group_members: int = 1, gain_scale: float = 1.0, gate: Optional[torch.Tensor] = None):
     """A router's choice for every token: logits = weight x in float (FFMA, whatever the dtypes), scores = softmax over
-    all experts (or ``sigmoid`` of each); the experts form ``groups`` equal groups of neighbours, a group's score is its
-    largest score, and only experts of the ``keep`` best groups can be chosen; the ``top`` largest of those are.
-    Returns (choice int32 [tokens, top], weights float32 [tokens, top]): the chosen experts' scores, divided by their
-    sum if ``renormalize``.  Ties go to the lower index."""
-    _cuda(x, weight)
-    _contig(x, weight)
+    all experts (or ``sigmoid`` of each).  The choice compares scores + ``correction`` (float32, one an expert; None:
+    the scores): the experts form ``groups`` equal groups of neighbours, a group's score is the sum of its
+    ``group_members`` largest (1: its largest), and only experts of the ``keep`` best groups can be chosen; the ``top``
+    largest of those are.  Returns (choice int32 [tokens, top], weights float32 [tokens, top]): the chosen experts'
+    scores (without the correction), divided by their sum if ``renormalize``, times ``gain_scale``.  Ties go to the
+    lower index.  ``gate`` (one more row [1, width] of the weight's dtype): a third result, sigmoid(gate x) as float32
+    [tokens], summed like a logit."""
+    _cuda(x, weight, correction, gate)
+    _contig(x, weight, correction, gate)
+    _f32(correction)
     tokens, width = x.shape
     experts = weight.shape[0]
-    if weight.shape[1] != width or scores not in ("softmax", "sigmoid"):
-        raise KernelError("expert_router: the router's matrix does not fit, or unknown scores")
+    if weight.shape[1] != width or scores not in ("softmax", "sigmoid") or \
+            (correction is not None and correction.numel() != experts) or \
+            (gate is not None and (gate.numel() != width or gate.dtype != weight.dtype)):
+        raise KernelError("expert_router: the router's matrix, correction or gate does not fit, or unknown scores")
     choice = torch.empty((tokens, top), dtype=torch.int32, device=x.device)
     gains = torch.empty((tokens, top), dtype=torch.float32, device=x.device)
+    gate_out = torch.empty((tokens,), dtype=torch.float32, device=x.device) if gate is not None else None
     rc = load_cuda_library("experts.cu").b200_expert_router(
         _p(x), _code(x), _p(weight), _code(weight), tokens, width, experts, int(groups), int(keep), int(top),
-        int(scores == "sigmoid"), int(bool(renormalize)), _p(choice), _p(gains), _stream())
+        int(scores == "sigmoid"), int(bool(renormalize)), _p(correction), int(group_members),
+        ctypes.c_float(gain_scale), _p(gate), _p(gate_out), _p(choice), _p(gains), _stream())
     _ok(rc, "expert_router")
-    return choice, gains
+    return (choice, gains) if gate is None else (choice, gains, gate_out)
 
 
 def routed_experts(x: torch.Tensor, choice: torch.Tensor, gains: torch.Tensor, gate_up: torch.Tensor,
                    down: torch.Tensor, glu: str = "silu", limit: float = 0.0, alpha: float = 1.0,
-                   add: Optional[torch.Tensor] = None, tensor_memory: Optional[bool] = None) -> torch.Tensor:
-    """out[t] = sum_k gains[t, k] down[e] glu(gate[e] x_t, up[e] x_t) (+ add[t]), e = choice[t, k]; float32
+                   add: Optional[torch.Tensor] = None, tensor_memory: Optional[bool] = None,
+                   add_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = sum_k gains[t, k] down[e] glu(gate[e] x_t, up[e] x_t) (+ add_scale[t] * add[t]), e = choice[t, k]; float32
     [tokens, width].  ``glu``: "silu" (silu(g) u) or "clamped_swish" (g' sigmoid(alpha g') (u' + 1), g' = min(g, limit),
     u' = clamp(u, -limit, limit)).  ``add`` [tokens, width] (float32 or x's dtype) joins the sum in float: what every
-    token gets besides its experts.  Weights and the choice of product kernels as in ``table_experts``."""
-    _cuda(x, choice, gains, gate_up, down, add)
-    _contig(x, choice, gains, gate_up, down, add)
+    token gets besides its experts, times ``add_scale`` (float32 [tokens]; None: 1).  Weights and the choice of product
+    kernels as in ``table_experts``."""
+    _cuda(x, choice, gains, gate_up, down, add, add_scale)
+    _contig(x, choice, gains, gate_up, down, add, add_scale)
     _i32(choice)
-    _f32(gains)
+    _f32(gains, add_scale)
+    if add_scale is not None and (add is None or add_scale.numel() != x.shape[0]):
+        raise KernelError("routed_experts: add_scale needs add and one factor a token")
     tokens, width = x.shape
     top = choice.shape[1]
     if glu not in GLU_KINDS or tuple(choice.shape) != (tokens, top) or tuple(gains.shape) != (tokens, top) or \
@@ -1865,13 +1920,15 @@ def routed_experts(x: torch.Tensor, choice: torch.Tensor, gains: torch.Tensor, g
         xs = torch.empty((pairs, width), dtype=x.dtype, device=x.device)
         rc = load_cuda_library("experts_tcgen05.cu").b200_routed_experts_tcgen05(
             _p(x), _p(choice), _p(gains), top, experts, _p(gate_up), _p(down), tokens, width, ff, GLU_KINDS[glu],
-            ctypes.c_float(limit), ctypes.c_float(alpha), _p(add), add_code, _p(xs), _p(h), _p(y), _p(route), _p(out),
+            ctypes.c_float(limit), ctypes.c_float(alpha), _p(add), add_code, _p(add_scale), _p(xs), _p(h), _p(y),
+            _p(route), _p(out),
             _p(error_word(x.device)), _stream())
         _ok(rc, "routed_experts_tcgen05", 5)
         return out
     rc = lib.b200_routed_experts(_p(x), _code(x), _p(choice), _p(gains), top, experts, _p(gate_up), _p(down), tokens,
                                  width, ff, GLU_KINDS[glu], ctypes.c_float(limit), ctypes.c_float(alpha), _p(add),
-                                 add_code, _p(h), _p(y), _p(route), _p(out), _p(error_word(x.device)), _stream())
+                                 add_code, _p(add_scale), _p(h), _p(y), _p(route), _p(out), _p(error_word(x.device)),
+                                 _stream())
     _ok(rc, "routed_experts", 4)
     return out
 

@@ -283,6 +283,10 @@ class GroupedAttention(Part):
       * ``qk_norm_eps``: q and k are RMS-normed, ``qk_norm_scope`` "head": per head with one weight vector each
         (``q_norm``, ``k_norm`` of a head's size), "projection": over all of a token's q columns at once, before they
         are split into heads, and over all of its k columns (weights of the projections' sizes);
+        ``qk_norm_weight`` False: the per-head norm has no weights (x / sqrt(mean(x^2) + eps));
+        ``qk_norm_order`` "after_rotation": the per-head norm follows the rotation instead of preceding it;
+      * ``values_from_keys``: there is no value projection (the packed matrix holds q rows and k rows): a token's
+        value is its key as projected, before norm and rotation;
       * ``position_encoding`` / ``rot_dims``: the first rot_dims coordinates of every q and k head are rotated
         (the encoding says whether pairs are interleaved or half-split);
       * ``window`` W: a query at position p reads keys p - W < j <= p;  ``chunk`` C: only keys from p - p % C on
@@ -313,8 +317,19 @@ class GroupedAttention(Part):
         self.out_bias = bool(spec.get("out_bias", False))
         self.norm_scope = str(spec.get("qk_norm_scope", "head"))
         self.own_kv = bool(spec.get("own_kv", True))
+        self.norm_weight = bool(spec.get("qk_norm_weight", True))
+        self.norm_order = str(spec.get("qk_norm_order", "before_rotation"))
+        self.values_from_keys = bool(spec.get("values_from_keys", False))
         if self.norm_scope not in ("head", "projection"):
             raise ValueError(f"qk_norm_scope {self.norm_scope!r} is refused: head or projection")
+        if self.norm_order not in ("before_rotation", "after_rotation"):
+            raise ValueError(f"qk_norm_order {self.norm_order!r} is refused: before_rotation or after_rotation")
+        if self.norm_scope != "head" and (not self.norm_weight or self.norm_order != "before_rotation" or
+                                          self.values_from_keys):
+            raise ValueError("a norm without weights, a norm after the rotation and values that are the keys are "
+                             "served with per-head norms")
+        if self.values_from_keys and (self.dv != self.d or not self.own_kv):
+            raise ValueError("values that are the keys are as wide as the keys, and the layer has keys of its own")
         if self.nh % self.nkv:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         for width in (self.d, self.dv):
@@ -328,7 +343,8 @@ class GroupedAttention(Part):
         if self.rope is not None and (self.rot_dims != self.rope.rot_dim or self.rot_dims > self.d):
             raise ValueError("the rotation does not fit the head or the encoding")
         self.q_channels = self.nh * self.d
-        self.qkv_channels = self.q_channels + (self.nkv * (self.d + self.dv) if self.own_kv else 0)
+        self.qkv_channels = self.q_channels + (self.nkv * (self.d + (0 if self.values_from_keys else self.dv))
+                                               if self.own_kv else 0)
         self.bias_deferred = False
         self.zero_sinks = torch.zeros(self.nh, dtype=torch.float32, device=env.device) if self.zero_sink else None
 
@@ -339,7 +355,7 @@ class GroupedAttention(Part):
             decls["qkv_bias"] = ParamDecl((self.qkv_channels,), "vector")
         if self.out_bias:
             decls["o_bias"] = ParamDecl((self.hidden,), "vector")
-        if self.qk_eps is not None:
+        if self.qk_eps is not None and self.norm_weight:
             joint = self.norm_scope == "projection"
             decls["q_norm"] = ParamDecl((self.q_channels if joint else self.d,), "vector")
             if self.own_kv:
@@ -376,7 +392,9 @@ class GroupedAttention(Part):
         if cache.writes and not self.own_kv:
             raise RuntimeError("a layer without keys of its own must read the cache of another run-list entry")
         prepare = ops.joint_heads_prepare if self.norm_scope == "projection" else ops.heads_prepare
-        extra = {"has_kv": self.own_kv} if self.norm_scope == "projection" else {}
+        extra = {"has_kv": self.own_kv} if self.norm_scope == "projection" else \
+            {"plain_norm": self.qk_eps is not None and not self.norm_weight,
+             "norm_after_rotation": self.norm_order == "after_rotation", "values_are_keys": self.values_from_keys}
         prepare(packed, q, cache.k, cache.v, ctx.positions, slots, self.nh, self.nkv, self.d, self.dv,
                 bias=p.get("qkv_bias"), q_weight=p.get("q_norm"), k_weight=p.get("k_norm"),
                 eps=float(self.qk_eps or 0.0), inv_freq=rope.inv_freq if rope else None,
@@ -406,7 +424,11 @@ class LatentAttention(Part):
     so the cache holds ONE row per token, [c | k_rot] (kv_rank + rot_dim wide, one KV head for all query heads): it
     is the token's key, and its first kv_rank columns are the token's value (no value tensor is kept); a head's query is [W_uk[h]^T q_plain | q_rot] and its output W_uv[h] times the attention's
     result.  ``window``, ``chunk``, ``sink``, ``gate``, ``position_encoding`` / ``rot_dims``: as in
-    ``grouped_attention``."""
+    ``grouped_attention``; ``gate`` "head": one gate a head (heads gate rows instead of heads * v_head_dim).
+
+    ``q_rank`` R: the queries go through a latent of their own.  The packed projection then holds [R query latent |
+    kv_rank + rot_dim down projection | gate rows]; the query latent is RMS-normed (``q_latent_norm``, eps ``eps``)
+    and ``uq_proj`` [heads * (head_dim + rot_dim), R] gives the heads' query coordinates."""
     category = "mixer"
 
     def __init__(self, spec, env):
@@ -423,6 +445,8 @@ class LatentAttention(Part):
         self.scale = float(spec.get("softmax_scale", 1.0 / math.sqrt(self.d + self.r)))
         self.sink = bool(spec.get("sink", False))
         self.gate = bool(spec.get("gate", False))
+        self.gate_per_head = spec.get("gate") == "head"
+        self.q_rank = int(spec.get("q_rank") or 0)
         if (self.c + self.r) % 2 or self.c % 2 or self.c + self.r > 512:
             raise ValueError("kv_rank and kv_rank + rot_dim must be even and at most 512 (the attention kernels' head sizes)")
         name = spec.get("position_encoding")
@@ -431,21 +455,26 @@ class LatentAttention(Part):
         if self.rope is not None and (self.rot_dims != self.rope.rot_dim or self.rot_dims > self.r):
             raise ValueError("the rotation does not fit the rotated part or the encoding")
         self.q_channels = self.nh * (self.d + self.r)
-        self.gate_column = self.q_channels + self.c + self.r
+        self.down_column = self.q_rank if self.q_rank else self.q_channels
+        self.gate_column = self.down_column + self.c + self.r
+        self.gate_rows = (self.nh if self.gate_per_head else self.nh * self.dv) if self.gate else 0
         self.uk_t = None
 
     def param_decls(self):
-        rows = self.gate_column + (self.nh * self.dv if self.gate else 0)
+        rows = self.gate_column + self.gate_rows
         decls = {"qdkv_proj": ParamDecl((rows, self.hidden)), "latent_norm": ParamDecl((self.c,), "vector"),
                  "uk_proj": ParamDecl((self.nh * self.d, self.c)), "uv_proj": ParamDecl((self.nh * self.dv, self.c)),
                  "o_proj": ParamDecl((self.hidden, self.nh * self.dv))}
         if self.sink:
             decls["sink"] = ParamDecl((self.nh,), "vector")
+        if self.q_rank:
+            decls["q_latent_norm"] = ParamDecl((self.q_rank,), "vector")
+            decls["uq_proj"] = ParamDecl((self.q_channels, self.q_rank))
         return decls
 
     def bind(self, name, tensor):
         super().bind(name, tensor)
-        if name in ("latent_norm", "sink"):
+        if name in ("latent_norm", "sink", "q_latent_norm"):
             self.params[name] = tensor.to(torch.float32).contiguous()
         elif name == "uk_proj":
             # per head transposed, [heads, kv_rank, head_dim]: the product q_plain W_uk[h] as rows times rows
@@ -462,15 +491,20 @@ class LatentAttention(Part):
         tokens = x.shape[0]
         rope = self.rope
         packed = ops.linear(x, p["qdkv_proj"])
-        q_plain = packed[:, :self.q_channels].view(tokens, self.nh, self.d + self.r)[:, :, :self.d].transpose(0, 1)
+        if self.q_rank:
+            queries = ops.linear(ops.columns_rms_norm(packed, self.q_rank, p["q_latent_norm"], self.eps), p["uq_proj"])
+        else:
+            queries = packed
+        q_plain = queries[:, :self.q_channels].view(tokens, self.nh, self.d + self.r)[:, :, :self.d].transpose(0, 1)
         q_lat = ops.head_products(q_plain, self.uk_t)                                   # [heads, tokens, kv_rank]
         width = self.c + self.r
         q = torch.empty((tokens, self.nh * width), dtype=packed.dtype, device=packed.device)
         slots = ctx.slots[cache.group] if cache.writes else None
-        ops.latent_prepare(packed, q_lat, q, cache.k, cache.v, p["latent_norm"], self.eps, ctx.positions, slots,
+        ops.latent_prepare(queries, q_lat, q, cache.k, cache.v, p["latent_norm"], self.eps, ctx.positions, slots,
                            self.nh, self.d, self.r, self.c, inv_freq=rope.inv_freq if rope else None,
                            rot_dims=self.rot_dims if rope else 0,
-                           interleaved=getattr(rope, "pairing", "half_split") == "interleaved")
+                           interleaved=getattr(rope, "pairing", "half_split") == "interleaved",
+                           down=packed[:, self.down_column:])
         o_lat = torch.empty((tokens, self.nh * self.c), dtype=packed.dtype, device=packed.device)
         _masked_attention(self, q, o_lat, ctx, cache, self.nh, 1, width, self.c, p.get("sink"), shared_values=True)
         out = torch.empty((tokens, self.nh * self.dv), dtype=packed.dtype, device=packed.device)
@@ -478,7 +512,7 @@ class LatentAttention(Part):
                           p["uv_proj"].view(self.nh, self.dv, self.c),
                           out=out.view(tokens, self.nh, self.dv).transpose(0, 1))
         if self.gate:
-            ops.sigmoid_gate_mul(out, packed, self.gate_column)
+            ops.sigmoid_gate_mul(out, packed, self.gate_column, per=self.dv if self.gate_per_head else 1)
         return ops.linear(out, p["o_proj"])
 
 

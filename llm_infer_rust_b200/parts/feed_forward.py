@@ -127,10 +127,12 @@ class RoutedExperts(Part):
     """A mixture of gated experts chosen by a router, with an optional shared expert that every token takes:
 
         z = router x (in float);  s = softmax(z) over all experts (``scores`` "sigmoid": a sigmoid of each)
-        experts form ``groups`` equal groups of neighbours; a group's score is its largest s; only experts of the
-        ``keep_groups`` best groups can be chosen; the ``top`` largest of those are, with weights s (divided by their
-        sum if ``renormalize``)
-        y = sum_k s_k down[e_k] glu(gate[e_k] x, up[e_k] x)  +  shared_down glu(shared_gate x, shared_up x)
+        the choice compares c = s + correction (``correction``: a stored float an expert; else c = s)
+        experts form ``groups`` equal groups of neighbours; a group's score is the sum of its ``group_members``
+        largest c (1, the default: its largest); only experts of the ``keep_groups`` best groups can be chosen; the
+        ``top`` largest c of those are, with weights s (divided by their sum if ``renormalize``) times ``weight_scale``
+        y = sum_k s_k down[e_k] glu(gate[e_k] x, up[e_k] x)  +  a shared_down glu(shared_gate x, shared_up x)
+        a = 1, or with ``shared_gated`` sigmoid(shared_gate_row x): one number a token (``shared_gate_row`` [1, hidden])
 
     ``activation``: "swiglu" (silu(g) u) or "clamped_swish_glu" (g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit),
     u' = clamp(u, -limit, limit); ``alpha`` 1.702 unless given; the shared expert has its own ``shared_limit``).
@@ -156,6 +158,10 @@ class RoutedExperts(Part):
         self.alpha = float(spec.get("alpha") or 1.702)
         self.shared_inter = int(spec.get("shared_intermediate_size") or 0)
         self.shared_limit = float(spec.get("shared_limit") or 0.0)
+        self.correction = bool(spec.get("correction", False))
+        self.group_members = int(spec.get("group_members") or 1)
+        self.weight_scale = float(spec.get("weight_scale", 1.0))
+        self.shared_gated = bool(spec.get("shared_gated", False)) and self.shared_inter > 0
         if self.activation not in self._GLU:
             raise ValueError(f"activation {self.activation!r} is refused: {sorted(self._GLU)}")
         if self.experts % self.groups or not 1 <= self.keep <= self.groups or \
@@ -169,19 +175,32 @@ class RoutedExperts(Part):
         if self.shared_inter:
             decls["shared_gate_up_proj"] = ParamDecl((2 * self.shared_inter, self.hidden))
             decls["shared_down_proj"] = ParamDecl((self.hidden, self.shared_inter))
+        if self.shared_gated:
+            decls["shared_gate_row"] = ParamDecl((1, self.hidden))
+        if self.correction:
+            decls["correction"] = ParamDecl((self.experts,), "vector")
         return decls
+
+    def bind(self, name, tensor):
+        super().bind(name, tensor)
+        if name == "correction":
+            self.params[name] = tensor.to(torch.float32).contiguous()
 
     def forward(self, x):
         p = self.params
         glu = self._GLU[self.activation]
-        choice, gains = ops.expert_router(x, p["router"], self.top, self.groups, self.keep, self.scores, self.renormalize)
+        routed = ops.expert_router(x, p["router"], self.top, self.groups, self.keep, self.scores, self.renormalize,
+                                   correction=p.get("correction"), group_members=self.group_members,
+                                   gain_scale=self.weight_scale, gate=p.get("shared_gate_row"))
+        choice, gains = routed[0], routed[1]
+        shared_scale = routed[2] if self.shared_gated else None
         shared = None
         if self.shared_inter:
             a = ops.glu_columns(ops.linear(x, p["shared_gate_up_proj"]), glu, self.shared_limit, self.alpha)
             shared = ops.linear(a, p["shared_down_proj"])
         return ops.routed_experts(x, choice, gains, p["gate_up_proj"].view(self.experts, 2 * self.inter, self.hidden),
                                   p["down_proj"].view(self.experts, self.hidden, self.inter), glu, self.limit,
-                                  self.alpha, add=shared)
+                                  self.alpha, add=shared, add_scale=shared_scale)
 
 
 register_part("feed_forward", "swiglu", SwiGLU)
