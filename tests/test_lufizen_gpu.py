@@ -1,0 +1,515 @@
+"""Lufizen through the engine against the plain implementation (``plain_lufizen.py``), in float32 and bfloat16.
+
+Mechanisms alone (kernels against the plain functions, and one-layer models), whole prompts against token-by-token
+decoding, portions down to two tokens, batches of unequal requests against each alone, pages and slots that are freed
+and used again, keys that stand out far back and at page borders, the sink, the first tokens, long decoding, greedy
+generation through the scheduler, and trace replay through ``bin/trace_run``.
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import lufizen_kit as K
+import plain_lufizen as P
+
+pytestmark = pytest.mark.gpu
+
+PORTIONS = [2, 37, 3, 16, 64, 5, 1, 22]
+
+
+def cut(total, sizes):
+    out, k = [], 0
+    while total > 0:
+        n = min(total, sizes[k % len(sizes)])
+        out.append(n)
+        total -= n
+        k += 1
+    return out
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    """name -> (config, weights, folder stored in bfloat16)."""
+    out = {}
+    named = dict(K.CONFIGS, attention=K.ONLY_ATTENTION, latent=K.ONLY_LATENT, one=K.ONE_EXPERT)
+    for i, (name, raw) in enumerate(named.items()):
+        w = K.random_weights(raw, 500 + i)
+        out[name] = (raw, w, K.write_model(str(tmp_path_factory.mktemp("lufizen_" + name)), raw, w))
+    return out
+
+
+def _i32(x, dev="cuda"):
+    return torch.tensor(x, dtype=torch.int32, device=dev)
+
+
+# ----------------------------------------------------------------------------- mechanisms alone
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,G,d,rot,pairing,stretch", [(4, 2, 12, 8, "half", True), (3, 3, 16, 16, "half", False),
+                                                       (6, 1, 10, 0, "half", False), (2, 1, 160, 30, "half", True),
+                                                       (5, 1, 8, 4, "interleaved", False)])
+def test_rotation_then_plain_norm_and_values_that_are_the_projected_keys(H, G, d, rot, pairing, stretch, dtype):
+    """q and k are rotated (with stretched frequencies), THEN divided by their root mean square a head, without a
+    weight; the value that goes to the cache is the key as it was projected; into scrambled cache slots."""
+    from llm_infer_rust_b200.kernels import ops
+    dev = torch.device("cuda")
+    g = torch.Generator().manual_seed(H * 100 + d)
+    T, page, eps = 21, 4, 1e-3
+    nq, nk = H * d, G * d
+    packed = torch.randn(T, nq + nk + 5, generator=g) * 2                         # columns behind k are ignored
+    packed[3, nq:nq + d] *= 0.01                                                   # a small key: eps shows in its norm
+    packed = K.bf16_values(packed)
+    positions = torch.randint(0, 3000, (T,), generator=g)
+    spec = {"base": 1000.0, "dims": max(rot, 2)}
+    if stretch:
+        spec["scaling"] = {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 128}
+    f = P.frequencies(spec)
+
+    def prepared(x, heads):
+        x = x.reshape(T, heads, d)
+        if rot:
+            x = torch.cat([P.rotate(x[t:t + 1], f, pairing, first_position=int(positions[t]), angle_dtype=torch.float32)
+                           for t in range(T)])
+        return P.rms_norm(x, None, eps)
+
+    pd = packed.double()
+    want_q, want_k = prepared(pd[:, :nq], H), prepared(pd[:, nq:nq + nk], G)
+    want_v = pd[:, nq:nq + nk].reshape(T, G, d)
+    pages = -(-T // page)
+    slots = torch.randperm(pages * page, generator=g)[:T] + page                   # page 0 is never written
+    k_cache = torch.full((pages + 1, G, page, d), 9.0, device=dev, dtype=dtype)
+    v_cache = torch.full((pages + 1, G, page, d), 9.0, device=dev, dtype=dtype)
+    q = torch.empty((T, nq), device=dev, dtype=dtype)
+    ops.heads_prepare(packed.to(dev, dtype), q, k_cache, v_cache, _i32(positions.tolist()), _i32(slots.tolist()), H, G, d, d,
+                      eps=eps, inv_freq=f.float().to(dev) if rot else None, rot_dims=rot,
+                      interleaved=pairing == "interleaved", plain_norm=True, norm_after_rotation=True,
+                      values_are_keys=True)
+    tol = 2e-5 if dtype == torch.float32 else 1.2e-2
+    torch.testing.assert_close(q.cpu().double().reshape(T, H, d), want_q, rtol=tol, atol=tol)
+    for t in range(T):
+        p, o = divmod(int(slots[t]), page)
+        torch.testing.assert_close(k_cache[p, :, o].cpu().double(), want_k[t], rtol=tol, atol=tol)
+        assert torch.equal(v_cache[p, :, o].cpu().double(), want_v[t])              # stored as projected: exact
+    assert float(k_cache[0].min()) == 9.0 and float(v_cache[0].min()) == 9.0
+    # the norm is no identity on the small key, and the value is not the normed key
+    assert (want_k[3, 0].abs().max() > 5 * want_v[3, 0].abs().max())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tokens,stride,width", [(9, 50, 18), (300, 137, 128), (5, 1030, 1024)])
+def test_norm_of_a_column_range(tokens, stride, width, dtype):
+    from llm_infer_rust_b200.kernels import ops
+    g = torch.Generator().manual_seed(tokens)
+    x = K.bf16_values(torch.randn(tokens, stride, generator=g) * 3)
+    w = 1 + 0.3 * torch.randn(width, generator=g)
+    got = ops.columns_rms_norm(x.cuda().to(dtype), width, w.cuda(), 1e-5)
+    want = P.rms_norm(x[:, :width].double(), w.double(), 1e-5)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert got.shape == (tokens, width) and got.is_contiguous()
+    torch.testing.assert_close(got.cpu().double(), want, rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_one_gate_a_head_and_one_a_column(dtype):
+    from llm_infer_rust_b200.kernels import ops
+    g = torch.Generator().manual_seed(1)
+    T, H, dv, before = 11, 5, 14, 23
+    a = K.bf16_values(torch.randn(T, H * dv, generator=g))
+    packed = K.bf16_values(torch.randn(T, before + H * dv + 3, generator=g) * 2)
+    tol = 1e-6 if dtype == torch.float32 else 1e-2
+    got = ops.sigmoid_gate_mul(a.cuda().to(dtype), packed.cuda().to(dtype), before, per=dv)
+    want = a.double().reshape(T, H, dv) * P.sigmoid(packed[:, before:before + H].double())[:, :, None]
+    torch.testing.assert_close(got.cpu().double(), want.reshape(T, H * dv), rtol=tol, atol=tol)
+    got = ops.sigmoid_gate_mul(a.cuda().to(dtype), packed.cuda().to(dtype), before)
+    want = a.double() * P.sigmoid(packed[:, before:before + H * dv].double())
+    torch.testing.assert_close(got.cpu().double(), want, rtol=tol, atol=tol)
+
+
+def test_embedding_and_logit_factors():
+    from llm_infer_rust_b200.kernels import ops
+    g = torch.Generator().manual_seed(2)
+    table = K.bf16_values(torch.randn(30, 44, generator=g))
+    ids = _i32([3, 29, 0, 3])
+    for dt in (torch.float32, torch.bfloat16):
+        got = ops.embedding(ids, table.cuda().to(dt), torch.float32, 17.25)
+        assert torch.equal(got.cpu(), table[[3, 29, 0, 3]] * 17.25)                # the product is exact in float here
+        assert torch.equal(ops.embedding(ids, table.cuda().to(dt), torch.float32).cpu(), table[[3, 29, 0, 3]])
+    z = torch.randn(7, 1001, generator=g)
+    assert torch.equal(ops.scale_floats(z.cuda().clone(), 0.3).cpu(), z * torch.tensor(0.3))
+
+
+def _route_on_gpu(z, corr, top, groups, keep, scale, members=2, gate_logit=None, dtype=torch.float32):
+    """The router kernel on logits that are given: x is the identity's rows, so W x = W's columns."""
+    from llm_infer_rust_b200.kernels import ops
+    T, E = z.shape
+    x = torch.eye(T, dtype=torch.float32)                   # token t is unit vector t: logit[t][e] = W[e][t]
+    W = z.t().contiguous()
+    gate = None if gate_logit is None else gate_logit.reshape(1, T).contiguous()
+    out = ops.expert_router(x.cuda().to(dtype), W.cuda().to(dtype), top, groups, keep, "sigmoid", False,
+                            correction=None if corr is None else corr.float().cuda(), group_members=members,
+                            gain_scale=scale, gate=None if gate is None else gate.cuda().to(dtype))
+    return [o.cpu() for o in out]
+
+
+def test_router_correction_groups_by_their_two_best_and_weights_by_hand():
+    logit = lambda p: math.log(p / (1 - p))
+    s = [0.50, 0.10, 0.30, 0.35, 0.45, 0.05]
+    z = torch.tensor([[logit(p) for p in s]] * 4, dtype=torch.float32)
+    zero = torch.zeros(6)
+    choice, gains = _route_on_gpu(z, zero, 2, 3, 1, 2.0)
+    assert choice[0].tolist() == [3, 2] and torch.allclose(gains[0], torch.tensor([0.70, 0.60]), atol=1e-6)
+    choice, gains = _route_on_gpu(z, zero, 2, 3, 1, 1.0, members=1)          # by the best member alone: the first group
+    assert choice[0].tolist() == [0, 1]
+    choice, gains = _route_on_gpu(z, torch.tensor([0, 0, 0, 0, 0, 1.0]), 2, 3, 1, 1.0)
+    assert choice[0].tolist() == [5, 4] and torch.allclose(gains[0], torch.tensor([0.05, 0.45]), atol=1e-6)
+    # every choice score below zero: a shut group stays shut
+    choice, _ = _route_on_gpu(z, torch.tensor([-3.0, -3, -2, -2, -5, -5]), 2, 3, 1, 1.0)
+    assert sorted(choice[0].tolist()) == [2, 3]
+    choice, _ = _route_on_gpu(z, None, 3, 1, 1, 1.0)
+    assert choice[0].tolist() == [0, 4, 3]
+    choice, gains, gate = _route_on_gpu(z, zero, 2, 3, 2, 1.0, gate_logit=torch.tensor([0.0, 1.0, -2.0, 30.0]))
+    assert choice[0].tolist() == [0, 3]
+    assert torch.allclose(gate, P.sigmoid(torch.tensor([0.0, 1.0, -2.0, 30.0], dtype=torch.float64)).float(), atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,E,top,groups,keep,width", [(40, 8, 3, 4, 2, 40), (333, 16, 4, 4, 3, 264), (7, 9, 2, 9, 5, 36),
+                                                       (50, 6, 6, 1, 1, 72), (150, 12, 1, 3, 1, 48), (9, 33, 5, 3, 2, 1000)])
+def test_router_against_the_plain_choice(T, E, top, groups, keep, width, dtype):
+    from llm_infer_rust_b200.kernels import ops
+    g = torch.Generator().manual_seed(T + E)
+    x = K.bf16_values(torch.randn(T, width, generator=g) * 2)
+    W = K.bf16_values(torch.randn(E, width, generator=g) * 0.5 * width ** -0.5)
+    sg = K.bf16_values(torch.randn(1, width, generator=g) * width ** -0.5)
+    corr = torch.randn(E, generator=g) * 0.3
+    z = x.double() @ W.double().t()
+    chosen, weight = P.route(z, corr.double(), top, groups, keep, 2.5)
+    margin = P.route_margin(z, corr.double(), top, groups, keep)
+    choice, gains, gate = ops.expert_router(x.cuda().to(dtype), W.cuda().to(dtype), top, groups, keep, "sigmoid", False,
+                                            correction=corr.cuda(), group_members=2, gain_scale=2.5, gate=sg.cuda().to(dtype))
+    clear = margin > 1e-4
+    assert clear.float().mean() > 0.9
+    assert torch.equal(choice.cpu()[clear].long(), chosen[clear])
+    torch.testing.assert_close(gains.cpu()[clear].double(), weight[clear], rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(gate.cpu().double(), P.sigmoid(x.double() @ sg.double().t())[:, 0], rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype,tensor_memory", [(torch.float32, None), (torch.bfloat16, False), (torch.bfloat16, True)])
+@pytest.mark.parametrize("T", [5, 300])
+def test_experts_with_a_gated_share_for_every_token(T, dtype, tensor_memory):
+    """The weighted sum of the chosen experts plus add_scale[t] * add[t], on every kind of product."""
+    from llm_infer_rust_b200.kernels import ops
+    if tensor_memory and T * 2 < 128:
+        pytest.skip("the tcgen05 products take 128 pairs or more")
+    g = torch.Generator().manual_seed(T)
+    E, top, width, ff = 6, 2, 64, 24
+    x = K.bf16_values(torch.randn(T, width, generator=g))
+    gu = K.bf16_values(torch.randn(E, 2 * ff, width, generator=g) * width ** -0.5)
+    dn = K.bf16_values(torch.randn(E, width, ff, generator=g) * ff ** -0.5)
+    choice = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).int()
+    gains = torch.rand(T, top, generator=g) * 2
+    add, add_scale = torch.randn(T, width, generator=g), torch.rand(T, generator=g)
+    want = (add * add_scale[:, None]).double()
+    for t in range(T):
+        for k in range(top):
+            e = int(choice[t, k])
+            h = P.silu(x[t].double() @ gu[e, :ff].double().t()) * (x[t].double() @ gu[e, ff:].double().t())
+            want[t] += gains[t, k].double() * (h @ dn[e].double().t())
+    got = ops.routed_experts(x.cuda().to(dtype), choice.cuda(), gains.cuda(), gu.cuda().to(dtype), dn.cuda().to(dtype),
+                             "silu", add=add.cuda(), add_scale=add_scale.cuda(), tensor_memory=tensor_memory)
+    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    torch.testing.assert_close(got.cpu().double(), want, rtol=tol, atol=tol)
+    plain = ops.routed_experts(x.cuda().to(dtype), choice.cuda(), gains.cuda(), gu.cuda().to(dtype), dn.cuda().to(dtype),
+                               "silu", add=add.cuda(), tensor_memory=tensor_memory)
+    assert (plain.cpu().double() - want).abs().max() > 0.1                       # the gate is no rounding matter
+
+
+# ----------------------------------------------------------------------------- models
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["L1", "L2", "L3", "attention", "latent", "one"])
+def test_whole_decoded_and_in_portions(name, dtype, models):
+    if name == "one" and dtype == "bfloat16":
+        pytest.skip("one expert a token: a near tie between two experts shows in full; compared in float32")
+    raw, w, folder = models[name]
+    T = 150
+    ids = K.tokens(raw["vocab"], T, 3)
+    want, close = K.oracle_and_close_calls(raw, w, ids)
+    eng = K.make_engine(folder, dtype, page_size=8, pool_tokens=256)
+    tol = K.tolerance(name, dtype)
+    K.check_clear(K.run_alone(eng, 1, ids, [T]), want, close, dtype, "whole", tol)
+    K.check_clear(K.run_alone(eng, 2, ids, [T - 40] + [1] * 40), want, close, dtype, "last 40 decoded", tol)
+    K.check_clear(K.run_alone(eng, 3, ids, cut(T, PORTIONS)), want, close, dtype, "in portions", tol)
+    K.check_clear(K.run_alone(eng, 4, ids[:24], [1] * 24), want[:24], close[:24], dtype, "token by token from the first", tol)
+    K.check_clear(K.run_alone(eng, 5, ids[:61], [2] * 30 + [1]), want[:61], close[:61], dtype, "two tokens at a time", tol)
+    assert eng.cache.manager.check() == ""
+
+
+@pytest.mark.parametrize("dim,heads,kv", [(24, 3, 1), (80, 4, 2), (96, 2, 1), (128, 4, 2), (256, 2, 1)])
+def test_head_sizes_of_every_kernel_family(dim, heads, kv, tmp_path):
+    """Head sizes beyond the fixed configurations': multiples of 16 up to 256 (tensor-core kernels in bfloat16) and one
+    that is none; an attention layer and a latent layer whose rows are as wide; whole, decoded and in portions."""
+    raw = K.config(83, 64, 1e-5, [
+        K.attention(heads, kv, dim, dim ** -0.5, (10000.0, dim - 8, K.STRETCH), mlp=K.moe(24, 4, 2, 1.5, None, 16)),
+        K.latent(heads, 16, 8, 24, dim - 8, 40, 0.2, 10000.0)])
+    T = 130
+    ids = K.tokens(raw["vocab"], T, dim)
+    w = K.clear_weights(raw, 900 + dim, ids)
+    folder = K.write_model(str(tmp_path / "m"), raw, w)
+    want, close = K.oracle_and_close_calls(raw, w, ids)
+    for dtype in ("float32", "bfloat16"):
+        eng = K.make_engine(folder, dtype, page_size=16, pool_tokens=256)
+        K.check_clear(K.run_alone(eng, 1, ids, [T]), want, close, dtype, "whole")
+        K.check_clear(K.run_alone(eng, 2, ids, [T - 50] + [1] * 50), want, close, dtype, "last 50 decoded")
+        K.check_clear(K.run_alone(eng, 3, ids, cut(T, [33, 2, 64, 7])), want, close, dtype, "in portions")
+        eng.check_kernel_errors()
+        del eng
+
+
+def test_every_layer_against_the_plain_stream(models):
+    """The float32 stream after every layer, whole and cut into portions."""
+    from llm_infer_rust_b200.engine import StepEntry
+    raw, w, folder = models["L1"]
+    ids = K.tokens(raw["vocab"], 60, 5)
+    layers = []
+    P.forward(raw, w, ids, dtype=torch.float64, layers_out=layers)
+    eng = K.make_engine(folder, "float32", page_size=8, pool_tokens=128)
+    caught = []
+    for block in eng.model.blocks:
+        def wrapped(h, residual, ctx, cache, inner=block.forward):
+            out = inner(h, residual, ctx, cache)
+            caught.append(out[0].detach().cpu().double().clone())
+            return out
+        block.forward = wrapped
+    eng.open_request(1)
+    for lo, hi in ((0, 33), (33, 35), (35, 60)):
+        eng.step([StepEntry(1, ids[lo:hi], [])])
+    n = len(raw["layers"])
+    for i in range(n):
+        got = torch.cat([caught[s * n + i] for s in range(3)])
+        torch.testing.assert_close(got, layers[i], rtol=3e-5, atol=3e-5, msg=lambda m, i=i: f"layer {i}: {m}")
+
+
+def drawn_config(seed):
+    """A configuration whose every size, option and layer order is drawn: any model of the design must run as it is."""
+    import random
+    rng = random.Random(seed)
+    even = lambda lo, hi: 2 * rng.randint(lo // 2, hi // 2)
+
+    def feed_forward():
+        if rng.random() < 0.2:
+            return None
+        groups = rng.choice([None, None, 2, 3, 4])
+        per = rng.randint(1, 4)
+        experts = per * (groups or rng.randint(2, 3))
+        keep = rng.randint(1, groups) if groups else None
+        if groups and keep * per < 2:
+            keep = 2
+        allowed = keep * per if groups else experts
+        top = rng.randint(2, allowed)            # two or more: the lesser of two nearly equal experts counts little
+        shared = rng.randint(8, 40) if rng.random() < 0.6 else None
+        return K.moe(rng.randint(8, 40), experts, top, rng.uniform(0.5, 3.0), (groups, keep) if groups else None, shared)
+
+    def stretch():
+        if rng.random() < 0.5:
+            return None
+        low = rng.choice([1.0, 2.0])
+        return (rng.choice([2.0, 4.0, 8.0]), low, low * rng.choice([2.0, 4.0]), rng.choice([32, 128, 1024]))
+
+    layers = []
+    for i in range(rng.randint(2, 5)):
+        if rng.random() < 0.4:
+            rot_dim = even(2, 16)
+            layers.append(K.latent(rng.randint(1, 5), even(4, 32), rot_dim, even(4, 40), even(8, 64), rng.randint(6, 48),
+                                   rng.uniform(0.1, 0.3), rng.choice([50.0, 10000.0, 300000.0]), mlp=feed_forward()))
+            continue
+        kv = rng.randint(1, 3)
+        dim = rng.choice([16, 32, 48, 64]) if rng.random() < 0.4 else even(4, 40)
+        rot = None if rng.random() < 0.2 else (rng.choice([50.0, 10000.0, 300000.0]), even(2, dim), stretch())
+        layers.append(K.attention(kv * rng.randint(1, 4), kv, dim, rng.uniform(0.1, 0.5), rot, mlp=feed_forward()))
+    return K.config(rng.randint(50, 300), even(24, 96), rng.choice([1e-5, 1e-6, 3e-4]), layers,
+                    embedding_scale=rng.uniform(0.5, 3.0), logit_scale=rng.uniform(0.2, 2.0))
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_configurations_drawn_at_random(seed, tmp_path):
+    raw = drawn_config(seed)
+    T = 90
+    ids = K.tokens(raw["vocab"], T, seed)
+    w = K.clear_weights(raw, 700 + seed, ids)
+    folder = K.write_model(str(tmp_path / "m"), raw, w)
+    want, close = K.oracle_and_close_calls(raw, w, ids)
+    for dtype in ("float32", "bfloat16"):
+        eng = K.make_engine(folder, dtype, page_size=(4, 8, 16)[seed % 3], pool_tokens=256)
+        K.check_clear(K.run_alone(eng, 1, ids, [T]), want, close, dtype, f"{seed} whole")
+        K.check_clear(K.run_alone(eng, 2, ids, [T - 30] + [1] * 30), want, close, dtype, f"{seed} last 30 decoded")
+        K.check_clear(K.run_alone(eng, 3, ids, cut(T, [2, 17, 3, 40, 1, 5])), want, close, dtype, f"{seed} in portions")
+        assert eng.cache.manager.check() == ""
+        del eng
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_far_keys_and_the_sink_with_sharp_scores(dtype, models):
+    """Prompts of hundreds of tokens over many pages; scores so sharp that the best key, wherever it lies (far back, on
+    a page's first or last place, the sequence's first token), takes nearly all of a position's weight, or the sink
+    does."""
+    for name in ("attention", "latent"):
+        raw, w, folder = models[name]
+        T = 500
+        ids = K.tokens(raw["vocab"], T, 11)
+        want = K.oracle(raw, w, ids)
+        if name == "attention":
+            # the sink shows: with every sink lowered by 4 the plain logits move by far more than any bound here
+            w2 = dict(w)
+            w2["l0.mix.sink"] = w["l0.mix.sink"] - 4.0
+            moved = np.abs(K.oracle(raw, w2, ids) - want).max(axis=1)
+            assert (moved > 0.5).mean() > 0.2
+        eng = K.make_engine(folder, dtype, page_size=16, pool_tokens=512)
+        tol = K.tolerance(name, dtype)
+        K.check(K.run_alone(eng, 1, ids, [T]), want, dtype, name + " whole", tol)
+        K.check(K.run_alone(eng, 2, ids, [T - 70, 37, 2] + [1] * 31), want, dtype, name + " tail decoded", tol)
+        K.check(K.run_alone(eng, 3, ids, cut(T, [127, 2, 16, 129, 15, 1 + 16 * 7])), want, dtype, name + " in portions", tol)
+        del eng
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kind", ["attention", "latent"])
+def test_one_key_made_to_stand_out_far_back_and_at_page_borders(kind, dtype, models, tmp_path):
+    """Weights and token ids are made so that the key at position ``far`` (the sequence's first token, a page's last
+    and first place, a place in the middle) fits the queries of a token that comes again right behind it, a page later
+    and hundreds of positions later (``lufizen_kit.standout_case``): those positions must find it, in a prompt, cut
+    right behind the key, and decoded alone.  That the key matters is checked on the plain side."""
+    raw, w, _ = models[kind]
+    T, page = 420, 16
+    for far in (0, 15, 16, 47):
+        ids, w2, places = K.standout_case(kind, raw, w, far, T, 70 + far)
+        want = K.oracle(raw, w2, ids)
+        other = list(ids)
+        other[far] = 0
+        moved = np.abs(K.oracle(raw, w2, other) - want).max(axis=1)[places]
+        assert (moved > 0.3).sum() >= len(places) // 2, f"{kind} far={far}: the far key does not show ({moved})"
+        folder = K.write_model(str(tmp_path / f"{kind}{far}"), raw, w2)
+        eng = K.make_engine(folder, dtype, page_size=page, pool_tokens=448)
+        tol = K.tolerance(kind, dtype)
+        K.check(K.run_alone(eng, 1, ids, [T]), want, dtype, f"{kind} far={far} whole", tol)
+        K.check(K.run_alone(eng, 2, ids, [far + 1, 2, page - 1] + [1] * 40 + [T - far - page - 42]), want, dtype,
+                f"{kind} far={far} cut behind the key", tol)
+        K.check(K.run_alone(eng, 3, ids, [T - 40] + [1] * 40), want, dtype, f"{kind} far={far} tail decoded", tol)
+        del eng
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["L1", "L2"])
+def test_mixed_batches_with_pages_and_slots_used_again(name, dtype, models):
+    """Up to three live requests of unequal length in a pool that holds far less than all of them: portions of some
+    beside decoded tokens of others, and every position's logits as alone."""
+    from llm_infer_rust_b200.engine import StepEntry
+    from replay_driver import mixed_schedule
+    raw, w, folder = models[name]
+    lengths = {"a": 90, "b": 37, "c": 120, "d": 5, "e": 64, "f": 101}
+    reqs = {r: (K.tokens(raw["vocab"], n, 20 + i), max(2, n - 12 - i)) for i, (r, n) in enumerate(lengths.items())}
+    want = {r: K.oracle_and_close_calls(raw, w, ids) for r, (ids, _) in reqs.items()}
+    eng = K.make_engine(folder, dtype, page_size=8, pool_tokens=320, max_requests=3)
+    got = {r: [] for r in reqs}
+    number = {r: i + 1 for i, r in enumerate(reqs)}
+    opened = set()
+    for entries, end in mixed_schedule(reqs, 320, seed=4, max_live=3):
+        batch = []
+        for r, toks, wanted in entries:
+            if r not in opened:
+                eng.open_request(number[r])
+                opened.add(r)
+            batch.append(StepEntry(number[r], list(toks), list(wanted)))
+        logits = eng.step(batch).cpu().numpy()
+        at = 0
+        for r, toks, _ in entries:
+            got[r].append(logits[at:at + len(toks)].copy())
+            at += len(toks)
+        for r in end:
+            eng.close_request(number[r])
+        assert eng.cache.manager.check() == ""
+    eng.check_kernel_errors()
+    for r in reqs:
+        K.check_clear(np.concatenate(got[r]), *want[r], dtype, f"request {r} in mixed batches")
+
+
+def test_pages_that_are_used_again_hold_nothing_of_their_last_user(models):
+    """One request at a time in a pool of a few pages: the second gets the pages that the first one left full."""
+    raw, w, folder = models["L1"]
+    eng = K.make_engine(folder, "float32", page_size=4, pool_tokens=64, max_requests=1)
+    first, second = K.tokens(raw["vocab"], 50, 1), K.tokens(raw["vocab"], 33, 2)
+    K.check(K.run_alone(eng, 1, first, [20, 30]), K.oracle(raw, w, first), "float32", "first user of the pages")
+    K.check(K.run_alone(eng, 2, second, [1, 1, 31]), K.oracle(raw, w, second), "float32", "second user of the pages")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(dtype, models):
+    raw, w, folder = models["L1"]
+    ids = K.tokens(raw["vocab"], 260, 8)
+    eng = K.make_engine(folder, dtype, page_size=16, pool_tokens=320)
+    K.check_clear(K.run_alone(eng, 1, ids, [6] + [1] * 254), *K.oracle_and_close_calls(raw, w, ids), dtype,
+                  "254 tokens decoded one by one")
+
+
+@pytest.mark.parametrize("dtype,graphs,portion_graphs", [("float32", 0, 0), ("bfloat16", 0, 0), ("bfloat16", 4, 0),
+                                                         ("bfloat16", 4, 64)])
+def test_greedy_generation_through_the_scheduler(dtype, graphs, portion_graphs, models):
+    """``Engine.generate``: prompts cut by the scheduler's token budget, more prompts than slots, decode graphs in
+    bfloat16, and graphs of prompt portions whose shape comes again.  float32: the tokens are the plain
+    implementation's; bfloat16: every generated token is one whose plain logit is within a small margin of the best."""
+    from llm_infer_rust_b200 import SamplingParams
+    raw, w, folder = models["L2"]
+    prompts = [K.tokens(raw["vocab"], n, 40 + n) for n in (5, 23, 1, 12, 30, 64, 50)]
+    eng = K.make_engine(folder, dtype, page_size=8, pool_tokens=512, max_requests=3, cuda_graph_bs=graphs,
+                        chunked_prefill_size=16, max_prefill_tokens_per_batch=16,
+                        prefill_cuda_graph_max_tokens=portion_graphs)
+    results = eng.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
+    eng.check_kernel_errors()
+    for prompt, res in zip(prompts, results):
+        assert len(res.tokens) == 12
+        logits = K.oracle(raw, w, prompt + res.tokens)
+        for i, tok in enumerate(res.tokens):
+            row = logits[len(prompt) - 1 + i]
+            margin = 1e-4 if dtype == "float32" else 0.05 * max(1.0, np.abs(row).max())
+            assert row[tok] >= row.max() - margin, f"token {i} of a prompt of {len(prompt)}: {tok} is not the best"
+
+
+def test_trace_replay_as_a_user_runs_it(models, tmp_path):
+    from replay_driver import Replay, run_alone
+    raw, w, folder = models["L3"]
+    ids = K.tokens(raw["vocab"], 70, 9)
+    want, close = K.oracle_and_close_calls(raw, w, ids)
+    for dtype in ("bfloat16", "float32"):
+        rp = Replay(folder, dtype, 128, str(tmp_path / dtype), raw["vocab"], ["--page-size", "8"])
+        try:
+            # the runner's path is what is tested here; the engine's numbers are held to the tighter bound above
+            K.check_clear(run_alone(rp, "x", ids, [33, 2, 3] + [1] * 32), want, close, dtype, "replay",
+                          1e-4 if dtype == "float32" else None)
+        finally:
+            assert rp.close() == 0
+
+
+def test_command_line_random_weights_mode(tmp_path):
+    """The command line writes a random Lufizen model from a configuration and serves it; the same folder through
+    ``Engine.generate`` gives the same tokens."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from llm_infer_rust_b200 import SamplingParams
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = tmp_path / "cfg.json"
+    cfg.write_text(json.dumps(K.CONFIGS["L1"]))
+    made = tmp_path / "made"
+    cmd = [sys.executable, "-m", "llm_infer_rust_b200", "--model-path", str(made), "--random-weights", "--config",
+           str(cfg), "--seed", "5", "--dtype", "float32", "--page-size", "4", "--max-total-tokens", "256",
+           "--max-running-req", "2", "--max-seq-len", "64", "--cuda-graph-bs", "0", "--prompt-ids", "1,2,3",
+           "--prompt-ids", "9,8,7,6,5", "--max-tokens", "6", "--ignore-eos"]
+    done = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr
+    lines = [json.loads(x) for x in done.stdout.strip().splitlines()]
+    assert sorted(os.listdir(made)) == ["config.json", "model.safetensors"]
+    eng = K.make_engine(str(made), "float32", page_size=4, pool_tokens=256, max_requests=2)
+    want = eng.generate([[1, 2, 3], [9, 8, 7, 6, 5]], SamplingParams(max_tokens=6, ignore_eos=True))
+    assert [x["output_ids"] for x in lines] == [r.tokens for r in want]
+    eng.check_kernel_errors()
