@@ -39,6 +39,11 @@ added to the softmax's denominator, layers that read another layer's keys and va
 a shared expert, a per-layer token input, norms on the sublayers' outputs over a float32 stream); its routed experts
 also stand beside Mukenex's.
 
+``--design lufizen`` does the same for Lufizen (attention whose values are the projected keys, with a plain norm after
+a stretched rotation and learned sinks; latent attention with queries through a latent and a gate a head; a router
+with a choice correction and groups ranked by their two best members; a gated shared expert), beside Torinex, the
+closest earlier design, and Qwen3.
+
 Peaks come from MEASURED_PEAKS.json beside this file when it is there.  Weights are random
 (drawn on the device), token ids are synthetic.  One GPU only.
 """
@@ -854,8 +859,245 @@ def torinex_kernel_table(size, peak):
     return out
 
 
+# ----------------------------------------------------------------------------- --design lufizen
+LUFIZEN_EXPERTS = dict(experts=16, top=4, groups=4, keep=2)
+
+
+def lufizen_ranks(size):
+    """(kv_rank, q_rank, rot_dim) of the latent layers: the key rows (kv_rank + rot_dim) stay within the attention
+    kernels' 512 columns."""
+    W = DESIGN_SIZES[size]["width"]
+    return (256, 768, 64) if W <= 1024 else (384, 1536, 64)
+
+
+def lufizen_config(size, layers):
+    """Three attention layers (values that are the projected keys, a rotation of half of every head with stretched
+    frequencies, learned sinks) and then a latent-attention layer (queries through a latent, a gate a head), in turn;
+    every layer with 16 routed experts (4 a token out of 2 of 4 groups, each an eighth of Qwen3's intermediate size)
+    and a gated shared expert of half that size: together the active parameters of Qwen3's feed-forward."""
+    z = DESIGN_SIZES[size]
+    H, G, d, I = z["heads"], z["kv_heads"], z["head_dim"], z["inter"]
+    rank, q_rank, r = lufizen_ranks(size)
+    e = LUFIZEN_EXPERTS
+    mlp = {"kind": "moe", "expert": {"ff": I // 8}, "shared": {"ff": I // 2},
+           "router": {"experts": e["experts"], "top": e["top"], "scale": 2.5,
+                      "groups": {"count": e["groups"], "keep": e["keep"]}}}
+    attn = {"type": "attention", "mlp": mlp,
+            "mixer": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5,
+                      "rot": {"base": 1e6, "dims": d // 2,
+                              "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    latent = {"type": "latent_attention", "mlp": mlp,
+              "mixer": {"heads": H, "dim": d, "rot_dim": r, "vdim": d, "kv_rank": rank, "q_rank": q_rank,
+                        "scale": (d + r) ** -0.5, "rot": {"base": 1e6, "dims": r}}}
+    return {"architecture": "Lufizen", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
+            "embedding": {"scale": z["width"] ** 0.5}, "logit_scale": 0.5,
+            "layers": [latent if i % 4 == 2 else attn for i in range(layers)]}
+
+
+def lufizen_kernel_table(size, peak):
+    """Every kernel of Lufizen alone, beside the like kernel of the closest designs (Torinex's prepare kernel, attention
+    with a sink, router and experts; Mukenex's latent attention; Qwen3's where there is no closer one), at one layer's
+    sizes: a prompt portion of 2,048 tokens and a decode step of 8 rows at 2,048 tokens (``frac`` as in
+    ``kernel_table``)."""
+    import types
+    import torch
+    from llm_infer_rust_b200.kernels import ops
+    from llm_infer_rust_b200.parts.attention import decode_splits
+    z = DESIGN_SIZES[size]
+    W, nh, nkv, d, I = z["width"], z["heads"], z["kv_heads"], z["head_dim"], z["inter"]
+    rank, q_rank, r = lufizen_ranks(size)
+    e = LUFIZEN_EXPERTS
+    E, top, groups, keep, ffe = e["experts"], e["top"], e["groups"], e["keep"], I // 8
+    dev, bf = torch.device("cuda"), torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    page, ctx_len, rows_dec = 16, 2048, 8
+    out = {}
+
+    def put(name, us, nbytes=None, flops=None, of="hbm"):
+        rec = {"us": round(us, 2)}
+        if nbytes is not None:
+            rec["gb_s"] = round(nbytes / us / 1e3, 1)
+            rec["frac"] = round(nbytes / us / 1e3 / peak["hbm_gbs"], 3)
+        if flops is not None:
+            rec["tflops"] = round(flops / us / 1e6, 2)
+            rec["frac"] = round(flops / us / 1e6 / peak["bf16_tflops"], 3)
+            rec["of"] = of
+        out[name] = rec
+
+    def step(rows):
+        cu, pos = [0], []
+        for prefix, n in rows:
+            cu.append(cu[-1] + n)
+            pos += list(range(prefix, prefix + n))
+        R = len(rows)
+        width = -(-max(p + n for p, n in rows) // page)
+        table = torch.arange(1, R * width + 1, dtype=torch.int32, device=dev).view(R, width).contiguous()
+        slots = [int(table[r_, (p + i) // page]) * page + (p + i) % page for r_, (p, n) in enumerate(rows) for i in range(n)]
+        return types.SimpleNamespace(
+            num_rows=R, cu_q=i32(cu), positions=i32(pos), prefix_len=i32([p for p, _ in rows]),
+            kv_len=i32([p + n for p, n in rows]), slots=i32(slots), table=table, rows=i32(list(range(R))),
+            tokens=cu[-1], pages=R * width + 1)
+
+    for phase, c in (("prefill", step([(0, ctx_len)])), ("decode", step([(ctx_len - 1, 1)] * rows_dec))):
+        T = c.tokens
+        # --- between the projection and attention: rotation, a plain norm a head, the projected key kept as the value
+        cq = (nh + nkv) * d
+        packed = (torch.randn(T, cq, device=dev) * 0.5).to(bf)
+        k_cache = torch.zeros(c.pages, nkv, page, d, dtype=bf, device=dev).normal_()
+        v_cache = torch.zeros(c.pages, nkv, page, d, dtype=bf, device=dev).normal_()
+        q = torch.empty(T, nh * d, dtype=bf, device=dev)
+        inv_half = torch.pow(torch.tensor(1e6), -torch.arange(0, d // 2, 2) / (d // 2)).to(dev)
+        moved = T * (cq * 2 + (nh + 2 * nkv) * d * 2)
+        put(f"{phase}.lufizen.heads_prepare", timed_alone(lambda: ops.heads_prepare(
+            packed, q, k_cache, v_cache, c.positions, c.slots, nh, nkv, d, d, eps=1e-5, inv_freq=inv_half,
+            rot_dims=d // 2, interleaved=False, plain_norm=True, norm_after_rotation=True, values_are_keys=True),
+            flush), moved)
+        cq3 = (nh + 2 * nkv) * d
+        packed3 = (torch.randn(T, cq3, device=dev) * 0.5).to(bf)
+        bias, qw, kw = torch.zeros(cq3, device=dev), torch.ones(nh * d, device=dev), torch.ones(nkv * d, device=dev)
+        inv_freq = torch.pow(torch.tensor(1e6), -torch.arange(0, d, 2) / d).to(dev)
+        put(f"{phase}.torinex.joint_heads_prepare", timed_alone(lambda: ops.joint_heads_prepare(
+            packed3, q, k_cache, v_cache, c.positions, c.slots, nh, nkv, d, d, bias=bias, q_weight=qw, k_weight=kw,
+            eps=1e-5, inv_freq=inv_freq, rot_dims=d, interleaved=True), flush), T * cq3 * 4)
+        cos, sin = torch.ones(4096, d // 2, device=dev), torch.zeros(4096, d // 2, device=dev)
+        hn = torch.ones(d, dtype=bf, device=dev)
+        put(f"{phase}.qwen3.qkv_post", timed_alone(lambda: ops.qkv_post(
+            packed3, q, k_cache, v_cache, hn, hn, 1e-6, cos, sin, d, c.positions, c.slots, nh, nkv, d), flush), T * cq3 * 4)
+        # --- the latent layer: the query latent's norm, the heads' small products, the prepare kernel
+        lq = nh * (d + r)
+        first = (torch.randn(T, q_rank + rank + r + nh, device=dev) * 0.5).to(bf)
+        qn = torch.ones(q_rank, device=dev)
+        put(f"{phase}.lufizen.columns_rms_norm", timed_alone(lambda: ops.columns_rms_norm(first, q_rank, qn, 1e-5), flush),
+            T * q_rank * 4)
+        xq = torch.randn(T, q_rank, device=dev).to(bf)
+        wq = torch.ones(q_rank, dtype=bf, device=dev)
+        put(f"{phase}.qwen3.rms_norm", timed_alone(lambda: ops.rms_norm(xq, wq, 1e-6), flush), T * q_rank * 4)
+        queries = (torch.randn(T, lq, device=dev) * 0.5).to(bf)
+        lk = torch.zeros(c.pages, 1, page, rank + r, dtype=bf, device=dev).normal_()
+        uk_t = (torch.randn(nh, rank, d, device=dev) * d ** -0.5).to(bf)
+        uv = (torch.randn(nh, d, rank, device=dev) * rank ** -0.5).to(bf)
+        q_plain = queries.view(T, nh, d + r)[:, :, :d].transpose(0, 1)
+        q_lat = ops.head_products(q_plain, uk_t)
+        put(f"{phase}.lufizen.head_products_uk", timed_alone(lambda: ops.head_products(q_plain, uk_t), flush),
+            flops=2.0 * T * nh * d * rank, of="bf16")
+        lqo = torch.empty(T, nh * (rank + r), dtype=bf, device=dev)
+        inv_r = torch.pow(torch.tensor(1e6), -torch.arange(0, r, 2) / r).to(dev)
+        lw = torch.ones(rank, device=dev)
+        put(f"{phase}.lufizen.latent_prepare", timed_alone(lambda: ops.latent_prepare(
+            queries, q_lat, lqo, lk, None, lw, 1e-5, c.positions, c.slots, nh, d, r, rank, inv_freq=inv_r, rot_dims=r,
+            down=first[:, q_rank:]), flush), T * (nh * (rank * 2 + r * 2) * 2 + (rank + r) * 2 * 2))
+        # --- attention: every earlier key with a learned sink; the latent's rows without one
+        o = torch.empty(T, nh * d, dtype=bf, device=dev)
+        lo = torch.empty(T, nh * rank, dtype=bf, device=dev)
+        sinks = torch.randn(nh, device=dev)
+        pairs_all = T * (T + 1) / 2
+        window = 1024                                              # Mukenex's latent layers read a window of that many
+        if phase == "prefill":
+            put("prefill.lufizen.attention_sink", timed_alone(lambda: ops.prefill_attention(
+                q, k_cache, v_cache, o, c.table, c.cu_q, c.kv_len, c.prefix_len, c.rows, 1, T, nh, nkv, d, page, None,
+                d ** -0.5, v_head_dim=d, precise_weights=True, sinks=sinks), flush, repeats=3),
+                flops=4.0 * nh * d * pairs_all, of="bf16")
+            put("prefill.torinex.attention_blocks_sink", timed_alone(lambda: ops.prefill_attention(
+                q, k_cache, v_cache, o, c.table, c.cu_q, c.kv_len, c.prefix_len, c.rows, 1, T, nh, nkv, d, page, None,
+                d ** -0.5, v_head_dim=d, precise_weights=True, chunk=window, sinks=sinks), flush, repeats=3),
+                flops=4.0 * nh * d * sum(p % window + 1 for p in range(T)), of="bf16")
+            put("prefill.qwen3.attention", timed_alone(lambda: ops.prefill_attention(
+                q, k_cache, v_cache, o, c.table, c.cu_q, c.kv_len, c.prefix_len, c.rows, 1, T, nh, nkv, d, page, None,
+                d ** -0.5), flush), flops=4.0 * nh * d * pairs_all, of="bf16")
+            put("prefill.lufizen.attention_latent", timed_alone(lambda: ops.prefill_attention(
+                lqo, lk, None, lo, c.table, c.cu_q, c.kv_len, c.prefix_len, c.rows, 1, T, nh, 1, rank + r, page, None,
+                (d + r) ** -0.5, v_head_dim=rank, precise_weights=True, shared_values=True), flush, repeats=3),
+                flops=2.0 * nh * (2 * rank + r) * pairs_all, of="bf16")
+            put("prefill.mukenex.attention_latent", timed_alone(lambda: ops.prefill_attention(
+                lqo, lk, None, lo, c.table, c.cu_q, c.kv_len, c.prefix_len, c.rows, 1, T, nh, 1, rank + r, page, window,
+                (d + r) ** -0.5, v_head_dim=rank, precise_weights=True, sinks=sinks, shared_values=True), flush, repeats=3),
+                flops=2.0 * nh * (2 * rank + r) * sum(min(p, window - 1) + 1 for p in range(T)), of="bf16")
+        else:
+            def decode(name, qq, kk, vv, oo, heads, kvh, dk, dv_, bound, nbytes, **kw):
+                plain = dk == dv_
+                per_split = ops.decode_ctas_per_split(bf, rows_dec, heads, kvh, dk, page, plain)
+                keys = 512
+                if kw.get("shared_values"):
+                    per_split = rows_dec * (heads // ops.latent_head_group(heads))
+                    keys = 128                                     # the engine's rule for latent rows
+                splits = decode_splits(per_split, bound, 148, keys)
+                need = ops.decode_scratch_floats(rows_dec, heads, max(dk, dv_), splits)
+                scratch = torch.empty(max(need, 1), device=dev)
+                win, scale = kw.pop("window_", None), kw.pop("scale_", dk ** -0.5)
+                put(name, timed_alone(lambda: ops.decode_attention(
+                    qq, kk, vv, oo, scratch, c.table, c.cu_q, c.kv_len, c.rows, rows_dec, heads, kvh, dk, page,
+                    win, scale, splits, **kw), flush), nbytes)
+            kv_all = rows_dec * ctx_len * nkv * d * 2 * 2
+            decode("decode.lufizen.attention_sink", q, k_cache, v_cache, o, nh, nkv, d, d, ctx_len, kv_all,
+                   v_head_dim=d, precise_weights=True, sinks=sinks)
+            decode("decode.torinex.attention_blocks_sink", q, k_cache, v_cache, o, nh, nkv, d, d, window,
+                   rows_dec * window * nkv * d * 2 * 2, v_head_dim=d, precise_weights=True, chunk=window, sinks=sinks)
+            decode("decode.qwen3.attention", q, k_cache, v_cache, o, nh, nkv, d, d, ctx_len, kv_all)
+            decode("decode.lufizen.attention_latent", lqo, lk, None, lo, nh, 1, rank + r, rank, ctx_len,
+                   rows_dec * ctx_len * (rank + r) * 2, v_head_dim=rank, precise_weights=True, shared_values=True)
+            decode("decode.mukenex.attention_latent", lqo, lk, None, lo, nh, 1, rank + r, rank, window,
+                   rows_dec * window * (rank + r) * 2, v_head_dim=rank, precise_weights=True, sinks=sinks,
+                   window_=window, shared_values=True)
+        lo_t = lo.view(T, nh, rank).transpose(0, 1)
+        lout = torch.empty(T, nh * d, dtype=bf, device=dev)
+        put(f"{phase}.lufizen.head_products_uv", timed_alone(lambda: ops.head_products(
+            lo_t, uv, out=lout.view(T, nh, d).transpose(0, 1)), flush), flops=2.0 * T * nh * d * rank, of="bf16")
+        # --- the gate: one a head, beside one a column
+        put(f"{phase}.lufizen.head_gate_mul", timed_alone(lambda: ops.sigmoid_gate_mul(
+            lout, first, q_rank + rank + r, per=d), flush), T * nh * d * 4)
+        gp = (torch.randn(T, 2 * nh * d, device=dev)).to(bf)
+        put(f"{phase}.mukenex.sigmoid_gate_mul", timed_alone(lambda: ops.sigmoid_gate_mul(o, gp, nh * d), flush), T * nh * d * 6)
+        # --- the residual (Torinex's kernel, unchanged) and the factor on the logits
+        stream = torch.randn(T, W, device=dev)
+        y = torch.randn(T, W, device=dev).to(bf)
+        wn = torch.ones(W, device=dev)
+        put(f"{phase}.lufizen.norm_add", timed_alone(lambda: ops.norm_add(stream, y, wn, 1e-5, cast_to=bf), flush), T * W * 12)
+        if phase == "decode":
+            lg = torch.randn(rows_dec, z["vocab"], device=dev)
+            put("decode.lufizen.scale_logits", timed_alone(lambda: ops.scale_floats(lg, 0.5), flush), rows_dec * z["vocab"] * 8)
+        # --- router and experts beside Torinex's and Qwen3's feed-forward with the same active parameters
+        xe = torch.randn(T, W, device=dev).to(bf)
+        wr = (torch.randn(E, W, device=dev) * W ** -0.5).to(bf)
+        sg = (torch.randn(1, W, device=dev) * W ** -0.5).to(bf)
+        corr = torch.randn(E, device=dev) * 0.1
+        route = lambda: ops.expert_router(xe, wr, top, groups, keep, "sigmoid", False, correction=corr, group_members=2,
+                                          gain_scale=2.5, gate=sg)
+        put(f"{phase}.lufizen.expert_router", timed_alone(route, flush), T * W * 2 + (E + 1) * W * 2 + T * (top * 8 + 4))
+        put(f"{phase}.torinex.expert_router", timed_alone(lambda: ops.expert_router(xe, wr, top, groups, keep), flush),
+            T * W * 2 + E * W * 2 + T * top * 8)
+        choice, gains, share_gate = route()
+        gate_up = (torch.randn(E, 2 * ffe, W, device=dev) * W ** -0.5).to(bf)
+        down = (torch.randn(E, W, ffe, device=dev) * ffe ** -0.5).to(bf)
+        share = torch.randn(T, W, device=dev).to(bf)
+        used = int(torch.unique(choice).numel())
+        for name, fn in (("lufizen", lambda: ops.routed_experts(xe, choice, gains, gate_up, down, "silu", add=share,
+                                                               add_scale=share_gate)),
+                         ("torinex", lambda: ops.routed_experts(xe, choice, gains, gate_up, down, "clamped_swish", 7.0,
+                                                               1.702, add=share))):
+            us = timed_alone(fn, flush)
+            if phase == "prefill":
+                put(f"prefill.{name}.routed_experts", us, flops=6.0 * T * top * W * ffe, of="bf16")
+            else:
+                put(f"decode.{name}.routed_experts", us, used * 3 * W * ffe * 2)
+        gs = torch.randn(T, I, device=dev).to(bf)                   # the shared expert's gate and up columns
+        put(f"{phase}.lufizen.glu_silu", timed_alone(lambda: ops.glu_columns(gs, "silu"), flush), T * I // 2 * 6)
+        put(f"{phase}.torinex.glu_clamped_swish", timed_alone(lambda: ops.glu_columns(gs, "clamped_swish", 7.0, 1.702), flush),
+            T * I // 2 * 6)
+        wgu = (torch.randn(2 * I, W, device=dev) * W ** -0.5).to(bf)
+        wdn = (torch.randn(W, I, device=dev) * I ** -0.5).to(bf)
+        us = timed_alone(lambda: ops.linear(ops.silu_mul(ops.linear(xe, wgu)), wdn), flush)
+        if phase == "prefill":
+            put("prefill.qwen3.feed_forward", us, flops=6.0 * T * W * I, of="bf16")
+        else:
+            put("decode.qwen3.feed_forward", us, 3 * W * I * 2)
+    return out
+
+
 DESIGNS = {"kefetar": (kefetar_config, kernel_table), "mukenex": (mukenex_config, mukenex_kernel_table),
-           "torinex": (torinex_config, torinex_kernel_table)}
+           "torinex": (torinex_config, torinex_kernel_table), "lufizen": (lufizen_config, lufizen_kernel_table)}
+# The closest earlier design, which stands beside the new one and Qwen3 at equal sizes.
+BESIDE = {"lufizen": ("torinex", torinex_config)}
 
 
 def design_main(args) -> int:
@@ -870,7 +1112,11 @@ def design_main(args) -> int:
                                    "sizes": {}, "kernels": {}}
     for size in [n for n in args.design_sizes.split(",") if n]:
         rec = {}
-        for name, raw in ((args.design, make_config(size, args.layers or 8)), ("qwen3", qwen3_config(size, args.layers or 8))):
+        arms = [(args.design, make_config(size, args.layers or 8))]
+        if args.design in BESIDE:
+            arms.append((BESIDE[args.design][0], BESIDE[args.design][1](size, args.layers or 8)))
+        arms.append(("qwen3", qwen3_config(size, args.layers or 8)))
+        for name, raw in arms:
             engine = design_engine(raw, 8, context)
             vocab = raw.get("vocab", raw.get("vocab_size"))
             ms = prefill_timed(engine, 2048, vocab)
@@ -907,9 +1153,9 @@ def main() -> int:
                     help="other shapes measured into `points` (decode at batch 1 / 8 / 64, prefill), comma separated")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one phase alone and print a short line (for profiling)")
-    ap.add_argument("--design", choices=["qwen3", "kefetar", "mukenex", "torinex"], default="qwen3",
-                    help="kefetar, mukenex, torinex: that design beside Qwen3 at equal sizes, and its kernels alone (another line)")
-    ap.add_argument("--design-sizes", default="1k,4k", help="layer sizes of --design kefetar / mukenex / torinex, comma separated")
+    ap.add_argument("--design", choices=["qwen3", "kefetar", "mukenex", "torinex", "lufizen"], default="qwen3",
+                    help="kefetar, mukenex, torinex, lufizen: that design beside Qwen3 at equal sizes, and its kernels alone (another line)")
+    ap.add_argument("--design-sizes", default="1k,4k", help="layer sizes of --design kefetar / mukenex / torinex / lufizen, comma separated")
     ap.add_argument("--no-kernels", action="store_true", help="--design ... without the table of single kernels")
     args = ap.parse_args()
     if args.design in DESIGNS and args.impl == "ours":

@@ -67,6 +67,8 @@ heads_prepare_kernel(const T* __restrict__ x, int in_stride, const float* __rest
                      const int* __restrict__ positions, const int* __restrict__ slots, int tokens, int nh, int nkv,
                      int d, int dv, int flags, int page_size, long long cache_slots, T* __restrict__ q_out,
                      T* __restrict__ k_cache, T* __restrict__ v_cache, int* err) {
+  pdl_launch_dependents();                          // the kernel after this one may be scheduled; it waits before it reads
+  pdl_wait();                                        // what this kernel reads belongs to the kernels before it
   __shared__ float buf[WARPS][MAX_VEC];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int vectors = nh + 2 * nkv;
@@ -129,6 +131,8 @@ latent_prepare_kernel(const T* __restrict__ x, int in_stride, const T* __restric
                       int interleaved, const int* __restrict__ positions, const int* __restrict__ slots, int tokens,
                       int nh, int d, int r, int c_dim, int page_size, long long cache_slots, T* __restrict__ q_out,
                       T* __restrict__ k_cache, T* __restrict__ v_cache, int* err) {
+  pdl_launch_dependents();                          // the kernel after this one may be scheduled; it waits before it reads
+  pdl_wait();                                        // what this kernel reads belongs to the kernels before it
   __shared__ float buf[WARPS][MAX_VEC];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int vectors = nh + 1;
@@ -321,12 +325,12 @@ B200_EXPORT int b200_heads_prepare(const void* x, int dtype, int in_stride, cons
   const long long work = static_cast<long long>(tokens) * (nh + 2 * nkv);
   const unsigned blocks = static_cast<unsigned>((work + WARPS - 1) / WARPS);
   if (dtype == B200_F32)
-    heads_prepare_kernel<float><<<blocks, WARPS * 32, 0, stream>>>(
+    return b200_launch(heads_prepare_kernel<float>, dim3(blocks), dim3(WARPS * 32), 0, stream, 0,
         static_cast<const float*>(x), in_stride, bias, q_w, k_w, eps, inv_freq, rot_dims, interleaved, positions, slots,
         tokens, nh, nkv, d, dv, flags, page_size, cache_slots, static_cast<float*>(q_out), static_cast<float*>(k_cache),
         static_cast<float*>(v_cache), err);
   else if (dtype == B200_BF16)
-    heads_prepare_kernel<__nv_bfloat16><<<blocks, WARPS * 32, 0, stream>>>(
+    return b200_launch(heads_prepare_kernel<__nv_bfloat16>, dim3(blocks), dim3(WARPS * 32), 0, stream, 0,
         static_cast<const __nv_bfloat16*>(x), in_stride, bias, q_w, k_w, eps, inv_freq, rot_dims, interleaved,
         positions, slots, tokens, nh, nkv, d, dv, flags, page_size, cache_slots, static_cast<__nv_bfloat16*>(q_out),
         static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), err);
@@ -349,15 +353,16 @@ B200_EXPORT int b200_latent_prepare(const void* x, int dtype, int in_stride, con
   const long long work = static_cast<long long>(tokens) * (nh + 1);
   const unsigned blocks = static_cast<unsigned>((work + WARPS - 1) / WARPS);
   if (dtype == B200_F32)
-    latent_prepare_kernel<float><<<blocks, WARPS * 32, 0, stream>>>(
+    return b200_launch(latent_prepare_kernel<float>, dim3(blocks), dim3(WARPS * 32), 0, stream, 0,
         static_cast<const float*>(x), in_stride, static_cast<const float*>(down), down_stride,
         static_cast<const float*>(q_lat), w_c, eps, inv_freq, rot_dims,
         interleaved, positions, slots, tokens, nh, d, r, c_dim, page_size, cache_slots, static_cast<float*>(q_out),
         static_cast<float*>(k_cache), static_cast<float*>(v_cache), err);
   else if (dtype == B200_BF16)
-    latent_prepare_kernel<__nv_bfloat16><<<blocks, WARPS * 32, 0, stream>>>(
+    return b200_launch(latent_prepare_kernel<__nv_bfloat16>, dim3(blocks), dim3(WARPS * 32), 0, stream, 0,
         static_cast<const __nv_bfloat16*>(x), in_stride, static_cast<const __nv_bfloat16*>(down), down_stride,
-        static_cast<const __nv_bfloat16*>(q_lat), w_c, eps, inv_freq, rot_dims, interleaved, positions, slots, tokens, nh, d, r, c_dim, page_size, cache_slots,
+        static_cast<const __nv_bfloat16*>(q_lat), w_c, eps, inv_freq, rot_dims, interleaved, positions, slots, tokens,
+        nh, d, r, c_dim, page_size, cache_slots,
         static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache),
         err);
   else

@@ -135,6 +135,8 @@ head_unit_norm_gate_kernel(T* __restrict__ out, const float* __restrict__ o, con
 template <typename T>
 __global__ void __launch_bounds__(256)
 sigmoid_gate_mul_kernel(T* out, const T* a, const T* __restrict__ g, int g_stride, int width, int per) {   // out may be a
+  pdl_launch_dependents();                          // the kernel after this one may be scheduled; it waits before it reads
+  pdl_wait();                                        // what this kernel reads belongs to the kernels before it
   const size_t t = blockIdx.x;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     const float x = to_f32<T>(g[t * g_stride + (per == 1 ? c : c / per)]);
@@ -190,15 +192,13 @@ B200_EXPORT int b200_sigmoid_gate_mul(void* out, const void* a, const void* g, i
   if (tokens <= 0) return 0;
   if (width <= 0 || per <= 0 || width % per) return B200_BAD_SIZE;
   if (dtype == B200_F32)
-    sigmoid_gate_mul_kernel<float><<<tokens, 256, 0, stream>>>(static_cast<float*>(out), static_cast<const float*>(a),
-                                                               static_cast<const float*>(g), g_stride, width, per);
-  else if (dtype == B200_BF16)
-    sigmoid_gate_mul_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(
-        static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(g),
-        g_stride, width, per);
-  else
-    return B200_BAD_DTYPE;
-  return b200_check_launch();
+    return b200_launch(sigmoid_gate_mul_kernel<float>, dim3(tokens), dim3(256), 0, stream, 0, static_cast<float*>(out),
+                       static_cast<const float*>(a), static_cast<const float*>(g), g_stride, width, per);
+  if (dtype == B200_BF16)
+    return b200_launch(sigmoid_gate_mul_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, 0,
+                       static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(a),
+                       static_cast<const __nv_bfloat16*>(g), g_stride, width, per);
+  return B200_BAD_DTYPE;
 }
 
 // ------------------------------------------------------------------ activations, a joint norm with a gate, a cap

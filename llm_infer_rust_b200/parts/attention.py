@@ -10,13 +10,18 @@ from .base import PagedKVSpec, ParamDecl, Part, StateSpec
 from .registry import register_part
 
 _KEYS_PER_CTA_AT_LEAST = 512      # fewer keys per CTA leave its warps' copy pipelines half empty
+# Latent rows are two to four times as wide as a head of 128 and one CTA serves up to 16 query heads on them: a CTA
+# is busy with far fewer keys (measured at 8 rows x 16 heads on rows of 320 columns, 2,048 keys: 43.0 us in 4 splits,
+# 27.5 us in 16; 32 heads on rows of 448: 128.0 against 91.1 us; one row of 8,192 keys: 246.8 against 82.9 us).
+_LATENT_KEYS_PER_CTA_AT_LEAST = 128
 
 
-def decode_splits(ctas_per_split: int, kv_len_bound: int, sm_count: int) -> int:
+def decode_splits(ctas_per_split: int, kv_len_bound: int, sm_count: int,
+                  keys_per_cta: int = _KEYS_PER_CTA_AT_LEAST) -> int:
     """How many CTAs share one row's keys.
 
     With ``ctas_per_split`` CTAs for each split, the number of splits is chosen so that the
-    grid fills whole waves of SMs as well as it can while every CTA keeps at least 512 keys.
+    grid fills whole waves of SMs as well as it can while every CTA keeps at least ``keys_per_cta`` keys.
     """
     ctas_per_split = max(1, ctas_per_split)
     if 8 * ctas_per_split >= 7 * sm_count:
@@ -25,7 +30,7 @@ def decode_splits(ctas_per_split: int, kv_len_bound: int, sm_count: int) -> int:
         # heads 90.8 us whole against 103.8 us in the four splits that fill the waves best, 64 rows 177.5 against
         # 182.3 us in two).
         return 1
-    most = max(1, min(64, kv_len_bound // _KEYS_PER_CTA_AT_LEAST))
+    most = max(1, min(64, kv_len_bound // max(1, keys_per_cta)))
     best, best_fill = 1, 0.0
     for splits in range(1, most + 1):
         if splits == 8 and 2 * ctas_per_split * splits > sm_count:
@@ -260,11 +265,13 @@ def _masked_attention(part, q, out, ctx, cache, num_heads, num_kv_heads, head_di
             if limit:
                 bound = min(bound, limit)
         plain = v_head_dim == head_dim
+        keys_per_cta = _KEYS_PER_CTA_AT_LEAST
         if shared_values and ops.latent_uses_tensor_cores(q.dtype, num_heads, head_dim, v_head_dim, page):
             per_split = ctx.num_decode * (num_heads // ops.latent_head_group(num_heads))
+            keys_per_cta = _LATENT_KEYS_PER_CTA_AT_LEAST
         else:
             per_split = ops.decode_ctas_per_split(q.dtype, ctx.num_decode, num_heads, num_kv_heads, head_dim, page, plain)
-        splits = decode_splits(per_split, bound, ctx.sm_count)
+        splits = decode_splits(per_split, bound, ctx.sm_count, keys_per_cta)
         need = ops.decode_scratch_floats(ctx.num_decode, num_heads, max(head_dim, v_head_dim), splits)
         scratch = ctx.scratch(need) if need else None
         ops.decode_attention(q, cache.k, cache.v, out, scratch, ctx.block_tables[g], ctx.cu_q,

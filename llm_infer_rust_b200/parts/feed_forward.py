@@ -186,6 +186,20 @@ class RoutedExperts(Part):
         if name == "correction":
             self.params[name] = tensor.to(torch.float32).contiguous()
 
+    def _shared_expert(self, x, glu):
+        """The shared expert's output.  Its SwiGLU form is the dense feed-forward's, and takes that part's fused
+        products: gate, up and silu(gate) * up in one few-row kernel for a step of few tokens, or as the epilogue of
+        the tcgen05 product for a large portion."""
+        p = self.params
+        w = p["shared_gate_up_proj"]
+        if glu == "silu" and x.dtype == torch.bfloat16:
+            if ops.few_row_takes(x.shape[0], w, self.env.dtype, ops.EPI_SWIGLU, norm=False):
+                return ops.linear(ops.few_row_linear(x, w, ops.EPI_SWIGLU), p["shared_down_proj"])
+            if ops.gemm_tc_pays(x, w, ops.GEMM_SWIGLU):
+                return ops.linear(ops.gemm_tc(x, w, ops.GEMM_SWIGLU), p["shared_down_proj"])
+        a = ops.glu_columns(ops.linear(x, w), glu, self.shared_limit, self.alpha)
+        return ops.linear(a, p["shared_down_proj"])
+
     def forward(self, x):
         p = self.params
         glu = self._GLU[self.activation]
@@ -194,10 +208,7 @@ class RoutedExperts(Part):
                                    gain_scale=self.weight_scale, gate=p.get("shared_gate_row"))
         choice, gains = routed[0], routed[1]
         shared_scale = routed[2] if self.shared_gated else None
-        shared = None
-        if self.shared_inter:
-            a = ops.glu_columns(ops.linear(x, p["shared_gate_up_proj"]), glu, self.shared_limit, self.alpha)
-            shared = ops.linear(a, p["shared_down_proj"])
+        shared = self._shared_expert(x, glu) if self.shared_inter else None
         return ops.routed_experts(x, choice, gains, p["gate_up_proj"].view(self.experts, 2 * self.inter, self.hidden),
                                   p["down_proj"].view(self.experts, self.hidden, self.inter), glu, self.limit,
                                   self.alpha, add=shared, add_scale=shared_scale)
