@@ -10,7 +10,7 @@
                       "groups": {"count", "keep"}}, "shared": {"ff"}}
                       (``groups`` absent: one group; ``shared`` absent: no shared expert)
 
-    attention         heads, kv_heads, dim, vdim (= dim: the values are the keys as projected), scale,
+    attention         heads, kv_heads, dim, vdim (= dim: the values are the keys as projected; may be absent), scale,
                       rot {base, dims, scaling {factor, low, high, original}} (``rot`` absent: no rotation;
                       ``scaling`` absent: the plain frequencies)
     latent_attention  heads, dim (unrotated query/key size), rot_dim (rotated size), vdim, kv_rank, q_rank, scale,
@@ -147,7 +147,9 @@ class LufizenConfig:
                 raise ConfigError(f"{where}mixer must be an object")
             kind, m, w = entry.get("type"), entry["mixer"], where + "mixer."
             ff = LufizenConfig._feed_forward(entry.get("mlp"), where)
-            heads, dim, vdim = _int(m, "heads", w), _int(m, "dim", w), _int(m, "vdim", w)
+            heads, dim = _int(m, "heads", w), _int(m, "dim", w)
+            # an attention layer's values are its keys: a file may leave their size out, but not contradict it
+            vdim = _int(m, "vdim", w) if (kind != "attention" or "vdim" in m) else dim
             scale = _number(m, "scale", w)
             if kind == "attention":
                 kv_heads = _int(m, "kv_heads", w)

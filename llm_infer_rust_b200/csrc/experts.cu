@@ -395,8 +395,9 @@ expert_combine_kernel(float* __restrict__ out, const float* __restrict__ Y, cons
 // of the `keep` best groups can be chosen (the others are shut out whatever their c, which may be negative), the `top`
 // largest c of them are.  The WEIGHTS are the chosen experts' s (without the correction), divided by their sum if
 // `renormalize`, times `gain_scale`.  Ties go to the lower index.
-// An extra row `gate_w` (null: none) gives gate_out[t] = sigmoid(gate_w . x[t]), summed like a logit: the gate of
-// something that every token takes besides its experts.
+// An extra row `gate_w` (null: none) gives gate_out[t] = sigmoid(gate_w . x[t]): the gate of something that every
+// token takes besides its experts.  All warps share that row (warp w takes every eighth piece of 256 columns; the
+// warps' sums are added in warp order), so that it does not cost one warp a second round of rows.
 // A block takes TT tokens (1 for a step of few tokens, so that they spread over the SMs; 4 otherwise): warp w
 // multiplies rows 2w, 2w + 1, then 2w + 16, .. for all of them (a row of W is read once a block), then warp t
 // chooses for token t.  A logit is summed the same way whatever the block holds: lane l takes columns
@@ -415,7 +416,8 @@ expert_router_kernel(const TX* __restrict__ x, const TW* __restrict__ W, int tok
   pdl_launch_dependents();                          // the kernel after this one may be scheduled; it waits before it reads
   pdl_wait();                                        // what this kernel reads belongs to the kernels before it
   extern __shared__ float rsm[];
-  const int zs = experts + 1;                                       // a token's logits, then the extra row's
+  __shared__ float gate_part[TT][ROUTER_WARPS];
+  const int zs = experts + 1;                                       // a token's logits (one spare place)
   float* z = rsm;                                                   // [TT][experts + 1]
   float* look = rsm + TT * zs;                                      // [TT][experts]: what the choice compares
   int* open = reinterpret_cast<int*>(look + TT * experts);          // [TT][experts]: may still be chosen
@@ -423,15 +425,47 @@ expert_router_kernel(const TX* __restrict__ x, const TW* __restrict__ W, int tok
   const int t0 = blockIdx.x * TT;
   const int nt = min(TT, tokens - t0);
   const bool wide = width % 8 == 0 && (gate_w == nullptr || reinterpret_cast<uintptr_t>(gate_w) % 16 == 0);
-  const int rows = experts + (gate_w != nullptr ? 1 : 0);
+  const int rows = experts;
+  if (gate_w != nullptr) {
+    float acc[TT];
+#pragma unroll
+    for (int i = 0; i < TT; ++i) acc[i] = 0.0f;
+    const TX* xs = x + static_cast<size_t>(t0) * width;
+    for (int k8 = lane * 8 + 256 * warp; k8 < width; k8 += 256 * ROUTER_WARPS) {
+      if (wide) {
+        float a[8];
+        load_floats<TW, 8>(gate_w + k8, a);
+#pragma unroll
+        for (int i = 0; i < TT; ++i) {
+          float v[8];
+          load_floats<TX, 8>(xs + static_cast<size_t>(min(i, nt - 1)) * width + k8, v);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[i] = fmaf(a[j], v[j], acc[i]);
+        }
+      } else {
+        const int end = min(k8 + 8, width);
+        for (int k = k8; k < end; ++k) {
+          const float a = to_f32<TW>(gate_w[k]);
+#pragma unroll
+          for (int i = 0; i < TT; ++i)
+            if (i < nt) acc[i] = fmaf(a, to_f32<TX>(xs[static_cast<size_t>(i) * width + k]), acc[i]);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < TT; ++i) {
+      const float v = warp_sum(acc[i]);
+      if (lane == 0) gate_part[i][warp] = v;
+    }
+  }
   for (int e0 = 2 * warp; e0 < rows; e0 += 2 * ROUTER_WARPS) {
     const bool two = e0 + 1 < rows;
     float acc[2][TT];
 #pragma unroll
     for (int i = 0; i < TT; ++i) acc[0][i] = acc[1][i] = 0.0f;
     const int e1 = two ? e0 + 1 : e0;
-    const TW* w0 = e0 < experts ? W + static_cast<size_t>(e0) * width : gate_w;
-    const TW* w1 = e1 < experts ? W + static_cast<size_t>(e1) * width : gate_w;
+    const TW* w0 = W + static_cast<size_t>(e0) * width;
+    const TW* w1 = W + static_cast<size_t>(e1) * width;
     const TX* xs = x + static_cast<size_t>(t0) * width;
     if (wide) {
 #pragma unroll 2
@@ -480,7 +514,11 @@ expert_router_kernel(const TX* __restrict__ x, const TW* __restrict__ W, int tok
   float* c = look + warp * experts;
   int* can = open + warp * experts;
   const int t = t0 + warp;
-  if (gate_w != nullptr && lane == 0) gate_out[t] = 1.0f / (1.0f + expf(-s[experts]));
+  if (gate_w != nullptr && lane == 0) {
+    float g = 0.0f;
+    for (int w = 0; w < ROUTER_WARPS; ++w) g += gate_part[warp][w];
+    gate_out[t] = 1.0f / (1.0f + expf(-g));
+  }
   if (sigmoid_scores) {
     for (int e = lane; e < experts; e += 32) s[e] = 1.0f / (1.0f + expf(-s[e]));
   } else {

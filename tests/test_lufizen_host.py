@@ -27,6 +27,10 @@ def test_the_architecture_is_found_by_its_name_and_every_size_comes_from_the_fil
         ("latent_attention", 3, 10, 4, 14, 24, 18, 4, None)
     assert (b.ff.groups, b.ff.keep, b.ff.shared_ff) == (1, 1, 0)
     assert d.rot is None and d.ff is None                  # what the file does not mention does not exist
+    import copy
+    bare = copy.deepcopy(raw)
+    bare["layers"][2]["mixer"].pop("vdim")                 # an attention layer's values are as wide as its keys
+    assert arch.parse_config(bare).layers[2].vdim == 10
     spec = arch.model_spec(c)
     assert [(e.layer, e.reads) for e in spec.run_list] == [(0, None), (1, None), (2, None), (3, None)]
     m0, m1, m2 = (spec.layers[i]["mixer"] for i in range(3))
