@@ -880,7 +880,7 @@ def lufizen_config(size, layers):
     rank, q_rank, r = lufizen_ranks(size)
     e = LUFIZEN_EXPERTS
     mlp = {"kind": "moe", "expert": {"ff": I // 8}, "shared": {"ff": I // 2},
-           "router": {"experts": e["experts"], "top": e["top"], "scale": 2.5,
+           "router": {"experts": e["experts"], "top": e["top"], "scale": 1.75,
                       "groups": {"count": e["groups"], "keep": e["keep"]}}}
     attn = {"type": "attention", "mlp": mlp,
             "mixer": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5,
@@ -890,7 +890,7 @@ def lufizen_config(size, layers):
               "mixer": {"heads": H, "dim": d, "rot_dim": r, "vdim": d, "kv_rank": rank, "q_rank": q_rank,
                         "scale": (d + r) ** -0.5, "rot": {"base": 1e6, "dims": r}}}
     return {"architecture": "Lufizen", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
-            "embedding": {"scale": z["width"] ** 0.5}, "logit_scale": 0.5,
+            "embedding": {"scale": 8.0}, "logit_scale": 0.25,
             "layers": [latent if i % 4 == 2 else attn for i in range(layers)]}
 
 
@@ -1055,14 +1055,14 @@ def lufizen_kernel_table(size, peak):
         put(f"{phase}.lufizen.norm_add", timed_alone(lambda: ops.norm_add(stream, y, wn, 1e-5, cast_to=bf), flush), T * W * 12)
         if phase == "decode":
             lg = torch.randn(rows_dec, z["vocab"], device=dev)
-            put("decode.lufizen.scale_logits", timed_alone(lambda: ops.scale_floats(lg, 0.5), flush), rows_dec * z["vocab"] * 8)
+            put("decode.lufizen.scale_logits", timed_alone(lambda: ops.scale_floats(lg, 0.25), flush), rows_dec * z["vocab"] * 8)
         # --- router and experts beside Torinex's and Qwen3's feed-forward with the same active parameters
         xe = torch.randn(T, W, device=dev).to(bf)
         wr = (torch.randn(E, W, device=dev) * W ** -0.5).to(bf)
         sg = (torch.randn(1, W, device=dev) * W ** -0.5).to(bf)
         corr = torch.randn(E, device=dev) * 0.1
         route = lambda: ops.expert_router(xe, wr, top, groups, keep, "sigmoid", False, correction=corr, group_members=2,
-                                          gain_scale=2.5, gate=sg)
+                                          gain_scale=1.75, gate=sg)
         put(f"{phase}.lufizen.expert_router", timed_alone(route, flush), T * W * 2 + (E + 1) * W * 2 + T * (top * 8 + 4))
         put(f"{phase}.torinex.expert_router", timed_alone(lambda: ops.expert_router(xe, wr, top, groups, keep), flush),
             T * W * 2 + E * W * 2 + T * top * 8)

@@ -67,9 +67,9 @@ CONFIGS = {
     # first and last, values narrower than keys, groups of one member
     "L2": config(211, 64, 1e-6, [
         latent(4, 16, 16, 8, 48, 32, 0.18, 500.0, mlp=moe(24, 3, 3, 1.5, None, 40)),
-        attention(8, 2, 32, 0.18, (500.0, 32), mlp=moe(32, 4, 2, 2.5, (4, 3), 16)),
+        attention(8, 2, 32, 0.18, (500.0, 32), mlp=moe(32, 4, 2, 2.25, (4, 3), 16)),
         attention(4, 4, 16, 0.3, (77.0, 2, (2.0, 1.0, 3.0, 32))),
-        latent(2, 32, 8, 48, 56, 80, 0.2, 50000.0, mlp=moe(24, 6, 4, 1.0, (2, 2))),
+        latent(2, 32, 8, 48, 56, 80, 0.2, 40000.0, mlp=moe(24, 6, 4, 1.0, (2, 2))),
     ], embedding_scale=1.0, logit_scale=2.0),
     # heads of 64 and wider than 128, one KV head, a latent wider than 128
     "L3": config(73, 72, 3e-6, [

@@ -184,10 +184,10 @@ def test_router_against_the_plain_choice(T, E, top, groups, keep, width, dtype):
     sg = K.bf16_values(torch.randn(1, width, generator=g) * width ** -0.5)
     corr = torch.randn(E, generator=g) * 0.3
     z = x.double() @ W.double().t()
-    chosen, weight = P.route(z, corr.double(), top, groups, keep, 2.5)
+    chosen, weight = P.route(z, corr.double(), top, groups, keep, 1.75)
     margin = P.route_margin(z, corr.double(), top, groups, keep)
     choice, gains, gate = ops.expert_router(x.cuda().to(dtype), W.cuda().to(dtype), top, groups, keep, "sigmoid", False,
-                                            correction=corr.cuda(), group_members=2, gain_scale=2.5, gate=sg.cuda().to(dtype))
+                                            correction=corr.cuda(), group_members=2, gain_scale=1.75, gate=sg.cuda().to(dtype))
     clear = margin > 1e-4
     assert clear.float().mean() > 0.9
     assert torch.equal(choice.cpu()[clear].long(), chosen[clear])
