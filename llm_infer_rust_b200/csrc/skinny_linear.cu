@@ -92,7 +92,17 @@ struct SkinnyParams {
   const float* stats_in;    // [stats_tiles][MMAX]; null: this product's prologue reads the rows itself
   int stats_tiles;
   long long* trace;         // for tuning (null in service): [4096 CTAs][32]: nanosecond clocks at the kernel's phases, then the SM's cycle counter at the same places
+  // QKV, further forms (all off: the above).  They are compiled in with -DSKINNY_QKV_FORMS only: a decode step runs
+  // this kernel's code once a warp and is bound by how fast that code arrives, so what the dense models never run
+  // stays out of their build (measured: 0.45 % of a Qwen3-0.6B decode step at batch 8 with the forms compiled in).
+  const float* inv_freq;    // [rot_dim / 2]: the angle of pair i is position * inv_freq[i], its cosine and sine taken here
+                            // (instead of cos_table / sin_table; any position)
+  int qkv_flags;            // QKV_PLAIN_NORM | QKV_NORM_AFTER_ROTATION | QKV_VALUES_ARE_KEYS
 };
+// QKV_PLAIN_NORM: q and k heads are normed without weights (x / sqrt(mean(x^2) + qk_eps)); QKV_NORM_AFTER_ROTATION: the
+// norm follows the rotation; QKV_VALUES_ARE_KEYS: the weight holds q and k heads only (N = (nh + nkv) * d) and a key
+// head's product, as it comes out, is also the token's value.
+enum : int { QKV_PLAIN_NORM = 1, QKV_NORM_AFTER_ROTATION = 2, QKV_VALUES_ARE_KEYS = 4 };
 
 // Compiled with -DSKINNY_TRACE (a tuning aid), the first thread of every CTA leaves both clocks at the kernel's phases.
 #ifdef SKINNY_TRACE
@@ -288,6 +298,19 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
       if (m < M) {
         if (p.slots != nullptr) epi_slot[rr] = p.slots[m];
         const int half = p.rot_dim / 2;
+#ifdef SKINNY_QKV_FORMS
+        if (p.inv_freq != nullptr && half > 0) {
+          const float pos = static_cast<float>(p.positions[m]);
+          epi_rotate[rr] = true;
+#pragma unroll
+          for (int j = 0; j < ROT_PER_LANE; ++j) {
+            const int i = lane + 32 * j;
+            epi_cos[rr][j] = 1.0f;
+            epi_sin[rr][j] = 0.0f;
+            if (i < half) sincosf(pos * p.inv_freq[i], &epi_sin[rr][j], &epi_cos[rr][j]);
+          }
+        } else
+#endif
         if (p.cos_table != nullptr && half > 0) {
           const int pos = p.positions[m];
           epi_rotate[rr] = pos >= 0 && pos < p.max_pos;
@@ -308,6 +331,13 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
 #pragma unroll
       for (int j = 0; j < 2 * MT; ++j) epi_w[j] = norm_weight(w, p.qk_w_f32, lane + 32 * j);
     }
+#ifdef SKINNY_QKV_FORMS
+    else if ((p.qkv_flags & QKV_PLAIN_NORM) != 0 && tile < p.nh + p.nkv) {
+      epi_norm = true;
+#pragma unroll
+      for (int j = 0; j < 2 * MT; ++j) epi_w[j] = 1.0f;
+    }
+#endif
   }
   // The norm's weights of this CTA's columns go to shared memory as floats (columns beyond K: zeros): they are the
   // same for every row and for every way of staging the rows below.
@@ -711,9 +741,49 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
           dst = (is_k ? p.k_cache : p.v_cache) + ((static_cast<size_t>(page) * p.nkv + kvh) * p.page_size + offset) * d;
         }
       }
+      const int half = p.rot_dim / 2;
+#ifdef SKINNY_QKV_FORMS
+      if (dst != nullptr && is_k && (p.qkv_flags & QKV_VALUES_ARE_KEYS) != 0) {
+        // the key as projected is the token's value: same page, same place, in the value cache
+        bf16* vdst = p.v_cache + (dst - p.k_cache);
+        for (int i = lane; i < d; i += 32) vdst[i] = __float2bfloat16_rn(row[i]);
+      }
+      const bool wanted = (p.cos_table != nullptr || p.inv_freq != nullptr) && half > 0;
+#else
+      const bool wanted = p.cos_table != nullptr && half > 0;
+#endif
       if (dst != nullptr && !is_q && !is_k) {
         for (int i = lane; i < d; i += 32) dst[i] = __float2bfloat16_rn(row[i]);
-      } else if (dst != nullptr) {
+      }
+#ifdef SKINNY_QKV_FORMS
+      else if (dst != nullptr && (p.qkv_flags & QKV_NORM_AFTER_ROTATION) != 0) {
+        if (wanted && !epi_rotate[rr] && lane == 0) atomicOr(p.err, B200_ERR_POSITION_RANGE);
+        if (wanted && epi_rotate[rr]) {                                      // in place: a lane's pairs are its own
+#pragma unroll
+          for (int j = 0; j < ROT_PER_LANE; ++j) {
+            const int i = lane + 32 * j;
+            if (i < half) {
+              const float a = row[i], b = row[i + half];
+              row[i] = a * epi_cos[rr][j] - b * epi_sin[rr][j];
+              row[i + half] = b * epi_cos[rr][j] + a * epi_sin[rr][j];
+            }
+          }
+          __syncwarp();
+        }
+        float scale = 1.0f;
+        if (epi_norm) {
+          float ss = 0.0f;
+#pragma unroll
+          for (int j = 0; j < 2 * MT; ++j) ss += row[lane + 32 * j] * row[lane + 32 * j];
+          ss = warp_sum(ss);
+          scale = rsqrtf(ss / static_cast<float>(d) + p.qk_eps);
+        }
+#pragma unroll
+        for (int j = 0; j < 2 * MT; ++j)
+          dst[lane + 32 * j] = __float2bfloat16_rn(epi_norm ? row[lane + 32 * j] * scale * epi_w[j] : row[lane + 32 * j]);
+      }
+#endif
+      else if (dst != nullptr) {
         if (epi_norm) {
           float ss = 0.0f;
 #pragma unroll
@@ -724,8 +794,6 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
           for (int j = 0; j < 2 * MT; ++j) row[lane + 32 * j] = row[lane + 32 * j] * scale * epi_w[j];
           __syncwarp();
         }
-        const int half = p.rot_dim / 2;
-        const bool wanted = p.cos_table != nullptr && half > 0;
         if (wanted && !epi_rotate[rr] && lane == 0) atomicOr(p.err, B200_ERR_POSITION_RANGE);
         if (wanted && epi_rotate[rr]) {
 #pragma unroll
@@ -892,7 +960,13 @@ B200_EXPORT int b200_skinny_linear(const void* w_map, const void* params, int he
   if (p.post_stats != nullptr && (p.mode != EPI_PLAIN_BF16 || bn > 128 || p.post_residual == nullptr || p.post_sum_out == nullptr))
     return B200_BAD_SIZE;
   if (p.stats_in != nullptr && (p.residual == nullptr || p.stats_tiles <= 0)) return B200_BAD_SIZE;
-  if (p.mode == EPI_QKV && (p.N != (p.nh + 2 * p.nkv) * head_dim || p.rot_dim < 0 || p.rot_dim > head_dim || (p.rot_dim & 1)))
+#ifdef SKINNY_QKV_FORMS
+  const int kv_tiles = (p.qkv_flags & QKV_VALUES_ARE_KEYS) != 0 ? p.nkv : 2 * p.nkv;
+#else
+  if (p.mode == EPI_QKV && (p.qkv_flags != 0 || p.inv_freq != nullptr)) return B200_BAD_SIZE;      // (not in this build)
+  const int kv_tiles = 2 * p.nkv;
+#endif
+  if (p.mode == EPI_QKV && (p.N != (p.nh + kv_tiles) * head_dim || p.rot_dim < 0 || p.rot_dim > head_dim || (p.rot_dim & 1)))
     return B200_BAD_SIZE;
   const int cols = p.mode == EPI_SWIGLU ? p.N / 2 : p.N;
   const int tile_cols = p.mode == EPI_SWIGLU ? bn / 2 : bn;

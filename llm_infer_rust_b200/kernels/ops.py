@@ -530,7 +530,7 @@ class _SkinnyParams(ctypes.Structure):
                 ("slots", ctypes.c_void_p), ("k_cache", ctypes.c_void_p), ("v_cache", ctypes.c_void_p),
                 ("err", ctypes.c_void_p), ("post_residual", ctypes.c_void_p), ("post_sum_out", ctypes.c_void_p),
                 ("post_stats", ctypes.c_void_p), ("stats_in", ctypes.c_void_p), ("stats_tiles", ctypes.c_int),
-                ("trace", ctypes.c_void_p)]
+                ("trace", ctypes.c_void_p), ("inv_freq", ctypes.c_void_p), ("qkv_flags", ctypes.c_int)]
 
 
 # For tuning: an int64 tensor [4096, 32] on the device; the first thread of every CTA of the next single-product
@@ -577,9 +577,15 @@ def _sm_count(device) -> int:
     return _sm_counts[key]
 
 
-def _skinny():
-    # (with a trace buffer set, the build that stamps its clocks: a tuning aid, compiled when first asked for)
-    lib = load_cuda_library("skinny_linear.cu", {"SKINNY_TRACE": 1} if skinny_trace is not None else None)
+def _skinny(qkv_forms: bool = False):
+    # (with a trace buffer set, the build that stamps its clocks: a tuning aid, compiled when first asked for;
+    # ``qkv_forms``: the build whose QKV epilogue knows the further forms, which the dense models' build leaves out)
+    defines = {}
+    if skinny_trace is not None:
+        defines["SKINNY_TRACE"] = 1
+    if qkv_forms:
+        defines["SKINNY_QKV_FORMS"] = 1
+    lib = load_cuda_library("skinny_linear.cu", defines or None)
     if not getattr(lib, "_checked", False):
         if lib.b200_skinny_params_size() != ctypes.sizeof(_SkinnyParams):
             raise KernelError("the parameter block of skinny_linear.cu and its Python mirror differ")
@@ -656,7 +662,10 @@ def skinny_linear(x, weight: torch.Tensor, mode: int = EPI_PLAIN_BF16, x_rows: O
     prologue and ``x.residual_out`` is filled).  ``mode``: EPI_PLAIN_BF16 / EPI_PLAIN_F32: the product;
     EPI_SWIGLU: silu(gate) * up for a weight of gate rows then up rows; EPI_QKV: per-head norm, rotary
     encoding and the cache store, with ``qkv`` = the keyword arguments of ``qkv_post`` (without ``qkv``);
-    the result is then ``q_out``.
+    the result is then ``q_out``.  Further keys of ``qkv``: ``inv_freq`` (float32 [rot_dim / 2]: angles are
+    position * inv_freq, their cosines and sines taken in the kernel, instead of the tables ``cos`` / ``sin``),
+    ``plain_norm`` (q and k heads normed without weights), ``norm_after_rotation``, ``values_are_keys`` (the weight
+    holds q and k heads only and a key head's product, as it comes out, is also stored as the token's value).
     """
     _flush_held()
     if isinstance(x, PendingNorm) and x.residual is None:
@@ -673,7 +682,8 @@ def skinny_linear(x, weight: torch.Tensor, mode: int = EPI_PLAIN_BF16, x_rows: O
     head_dim = qkv["head_dim"] if qkv else 0
     if not skinny_ok(m, weight, src.dtype, mode, head_dim):
         raise KernelError("the few-row product refuses this size or dtype")
-    lib = _skinny()
+    lib = _skinny(qkv_forms=bool(qkv) and (qkv.get("inv_freq") is not None or bool(qkv.get("plain_norm"))
+                                           or bool(qkv.get("norm_after_rotation")) or bool(qkv.get("values_are_keys"))))
     P = _SkinnyParams()
     P.x, P.x_rows = src.data_ptr(), (0 if rows_t is None else rows_t.data_ptr())
     if pending is not None:
@@ -697,9 +707,20 @@ def skinny_linear(x, weight: torch.Tensor, mode: int = EPI_PLAIN_BF16, x_rows: O
         qw, kw = qkv.get("q_weight"), qkv.get("k_weight")
         cos, sin = qkv.get("cos"), qkv.get("sin")
         slots = qkv.get("slots")
-        _cuda(out, kc, vc, qw, kw, cos, sin, qkv["positions"], slots)
-        if n != (nh + 2 * nkv) * head_dim or out.shape != (m, nh * head_dim) or out.dtype != torch.bfloat16:
+        inv_freq = qkv.get("inv_freq")
+        flags = (1 if qkv.get("plain_norm") else 0) | (2 if qkv.get("norm_after_rotation") else 0) | \
+            (4 if qkv.get("values_are_keys") else 0)
+        _cuda(out, kc, vc, qw, kw, cos, sin, qkv["positions"], slots, inv_freq)
+        _f32(inv_freq)
+        kv_tiles = nkv if flags & 4 else 2 * nkv
+        if n != (nh + kv_tiles) * head_dim or out.shape != (m, nh * head_dim) or out.dtype != torch.bfloat16:
             raise KernelError("qkv sizes do not fit the weight")
+        if inv_freq is not None and (cos is not None or inv_freq.numel() * 2 != int(qkv.get("rot_dim", 0))
+                                     or not inv_freq.is_contiguous()):
+            raise KernelError("frequencies come instead of tables, one for every rotated pair")
+        if flags & 4 and slots is not None and (vc is None or vc.shape != kc.shape or vc.dtype != kc.dtype):
+            raise KernelError("values that are the keys need a value cache of the key cache's shape")
+        P.inv_freq, P.qkv_flags = (0 if inv_freq is None else inv_freq.data_ptr()), flags
         if slots is not None and (kc is None or kc.dtype != torch.bfloat16 or kc.shape[1] != nkv or kc.shape[3] != head_dim):
             raise KernelError("the cache must be bfloat16 [pages + 1, kv_heads, page_size, head_dim]")
         if (qw is None) != (kw is None) or (qw is not None and qw.dtype != kw.dtype):
@@ -1059,7 +1080,9 @@ def few_row_linear(x, weight: torch.Tensor, mode: int = EPI_PLAIN_BF16, x_rows: 
     rows_t = pending.rows if pending is not None and pending.rows is not None else x_rows
     m = src.shape[0] if rows_t is None else rows_t.numel()
     head_dim = qkv["head_dim"] if qkv else 0
-    if few_row_route == "chain" and chain_takes(m, weight, src.dtype, mode, head_dim):
+    further = bool(qkv) and any(qkv.get(key) is not None and qkv.get(key) is not False
+                                for key in ("inv_freq", "plain_norm", "norm_after_rotation", "values_are_keys"))
+    if few_row_route == "chain" and not further and chain_takes(m, weight, src.dtype, mode, head_dim):
         out = _chain_append(pending, src, rows_t, m, weight, mode, qkv)
         if not lazy:
             flush_chain()

@@ -389,15 +389,43 @@ class GroupedAttention(Part):
     def state_spec(self):
         return None
 
+    def _fused_projection(self, tokens: int, x) -> bool:
+        """Whether a step of ``tokens`` tokens runs the projection, the rotation, the per-head norm and the cache
+        store in ONE few-row kernel (the dense models' fused QKV step, with this part's forms as its options): per-head
+        norms, no bias and no gate (the packed matrix holds nothing but heads), keys of its own as wide as the values,
+        half-split pairs, a head size that the kernel takes."""
+        if not (self.norm_scope == "head" and not self.bias and not self.gate and self.own_kv and self.dv == self.d
+                and x.dtype == torch.bfloat16 and ops.few_row_route != "chain"):
+            return False
+        if self.rope is not None and getattr(self.rope, "pairing", "half_split") != "half_split":
+            return False
+        return ops.few_row_takes(tokens, self.params["qkv_proj"], self.env.dtype, ops.EPI_QKV, self.d, norm=False)
+
     def forward(self, x, ctx, cache):
         p = self.params
         tokens = x.shape[0]
         rope = self.rope
+        if cache.writes and not self.own_kv:
+            raise RuntimeError("a layer without keys of its own must read the cache of another run-list entry")
+        if cache.writes and self._fused_projection(tokens, x):
+            q = torch.empty((tokens, self.nh * self.d), dtype=x.dtype, device=x.device)
+            ops.few_row_linear(x, p["qkv_proj"], ops.EPI_QKV, qkv=dict(
+                head_dim=self.d, num_heads=self.nh, num_kv_heads=self.nkv, q_out=q, k_cache=cache.k, v_cache=cache.v,
+                q_weight=p.get("q_norm"), k_weight=p.get("k_norm"), eps=float(self.qk_eps or 0.0),
+                inv_freq=rope.inv_freq if rope else None, rot_dim=self.rot_dims if rope else 0,
+                positions=ctx.positions, slots=ctx.slots[cache.group],
+                plain_norm=self.qk_eps is not None and not self.norm_weight,
+                norm_after_rotation=self.norm_order == "after_rotation", values_are_keys=self.values_from_keys))
+            out = torch.empty((tokens, self.nh * self.dv), dtype=x.dtype, device=x.device)
+            _masked_attention(self, q, out, ctx, cache, self.nh, self.nkv, self.d, self.dv,
+                              self.zero_sinks if self.zero_sink else p.get("sink"))
+            y = ops.linear(out, p["o_proj"])
+            if self.out_bias and not self.bias_deferred:
+                ops.add_row_bias(y, p["o_bias"])
+            return y
         packed = ops.linear(x, p["qkv_proj"])
         q = torch.empty((tokens, self.nh * self.d), dtype=packed.dtype, device=packed.device)
         slots = ctx.slots[cache.group] if cache.writes else None
-        if cache.writes and not self.own_kv:
-            raise RuntimeError("a layer without keys of its own must read the cache of another run-list entry")
         prepare = ops.joint_heads_prepare if self.norm_scope == "projection" else ops.heads_prepare
         extra = {"has_kv": self.own_kv} if self.norm_scope == "projection" else \
             {"plain_norm": self.qk_eps is not None and not self.norm_weight,

@@ -96,6 +96,59 @@ def test_rotation_then_plain_norm_and_values_that_are_the_projected_keys(H, G, d
     assert (want_k[3, 0].abs().max() > 5 * want_v[3, 0].abs().max())
 
 
+@pytest.mark.parametrize("M,H,G,d,rot,stretch,K_", [(1, 4, 2, 64, 32, True, 320), (8, 6, 1, 64, 64, False, 256),
+                                                     (16, 2, 2, 128, 64, True, 512), (5, 3, 1, 256, 30, False, 192),
+                                                     (3, 4, 4, 128, 0, False, 128)])
+def test_projection_rotation_plain_norm_and_store_in_one_few_row_kernel(M, H, G, d, rot, stretch, K_):
+    """A decode step's fused form: the packed q and k product, the rotation, the plain norm behind it and the cache
+    stores (the key, and the key as projected as the value) in ONE kernel, against the plain functions."""
+    from llm_infer_rust_b200.kernels import ops
+    dev = torch.device("cuda")
+    g = torch.Generator().manual_seed(M * 1000 + d)
+    page, eps = 4, 1e-5
+    x = K.bf16_values(torch.randn(M, K_, generator=g))
+    W = K.bf16_values(torch.randn((H + G) * d, K_, generator=g) * K_ ** -0.5)
+    positions = torch.randint(0, 3000, (M,), generator=g)
+    spec = {"base": 1000.0, "dims": max(rot, 2)}
+    if stretch:
+        spec["scaling"] = {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 128}
+    f = P.frequencies(spec)
+    y = x.double() @ W.double().t()
+
+    def prepared(z, heads):
+        z = z.reshape(M, heads, d)
+        if rot:
+            z = torch.cat([P.rotate(z[t:t + 1], f, "half", first_position=int(positions[t]), angle_dtype=torch.float32)
+                           for t in range(M)])
+        return P.rms_norm(z, None, eps)
+
+    want_q, want_k = prepared(y[:, :H * d], H), prepared(y[:, H * d:], G)
+    want_v = y[:, H * d:].reshape(M, G, d)
+    pages = -(-M // page) + 1
+    slots = torch.randperm(pages * page, generator=g)[:M] + page
+    k_cache = torch.full((pages + 1, G, page, d), 9.0, device=dev, dtype=torch.bfloat16)
+    v_cache = torch.full((pages + 1, G, page, d), 9.0, device=dev, dtype=torch.bfloat16)
+    q = torch.empty((M, H * d), device=dev, dtype=torch.bfloat16)
+    Wd = W.to(dev, torch.bfloat16)
+    assert ops.few_row_takes(M, Wd, torch.bfloat16, ops.EPI_QKV, d, norm=False)
+    ops.few_row_linear(x.to(dev, torch.bfloat16), Wd, ops.EPI_QKV, qkv=dict(
+        head_dim=d, num_heads=H, num_kv_heads=G, q_out=q, k_cache=k_cache, v_cache=v_cache, q_weight=None, k_weight=None,
+        eps=eps, inv_freq=f.float().to(dev) if rot else None, rot_dim=rot, positions=_i32(positions.tolist()),
+        slots=_i32(slots.tolist()), plain_norm=True, norm_after_rotation=True, values_are_keys=True))
+    ops.check_errors(dev)
+    tol = 1.5e-2
+    torch.testing.assert_close(q.cpu().double().reshape(M, H, d), want_q, rtol=tol, atol=tol)
+    for t in range(M):
+        p, o = divmod(int(slots[t]), page)
+        torch.testing.assert_close(k_cache[p, :, o].cpu().double(), want_k[t], rtol=tol, atol=tol)
+        torch.testing.assert_close(v_cache[p, :, o].cpu().double(), want_v[t], rtol=tol, atol=tol)
+    assert float(k_cache[0].min()) == 9.0 and float(v_cache[0].min()) == 9.0
+    untouched = torch.ones(pages + 1, page, dtype=torch.bool)
+    for t in range(M):
+        untouched[int(slots[t]) // page, int(slots[t]) % page] = False
+    assert bool((k_cache.cpu()[untouched.unsqueeze(1).expand(-1, G, -1)] == 9.0).all())
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("tokens,stride,width", [(9, 50, 18), (300, 137, 128), (5, 1030, 1024)])
 def test_norm_of_a_column_range(tokens, stride, width, dtype):
